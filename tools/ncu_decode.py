@@ -5,7 +5,7 @@ graph), so `ncu --nvtx --nvtx-include "profile/"` sees exactly those launches.
 
     ncu --nvtx --nvtx-include "profile/" --metrics gpu__time_duration.sum --clock-control none --csv \\
         --log-file gpurun_out/r02_cfg2_launches.csv python tools/ncu_decode.py --workload cfg2 --steps 2
-    ncu --nvtx --nvtx-include "profile/" --set full --clock-control none --import-source on -k regex:gemv_kernel -c 5 \\
+    ncu --nvtx --nvtx-include "profile/" --set full --clock-control none -k regex:gemv_kernel -c 5 \\
         -o gpurun_out/r02_gemv_fp16 python tools/ncu_decode.py --workload cfg2 --steps 1
     ... --fused 1 -k regex:decode_step -c 1       # the persistent whole-step kernel
     ... --prefill --layers 2                      # BASELINE configs[3]: SmoothQuant prefill, batch 8 x 2048"""

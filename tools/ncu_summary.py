@@ -34,7 +34,7 @@ def full(path, out):
     hdr, units = rows[0], rows[1]
     idx = [hdr.index(w) for w in WANT if w in hdr]
     with open(out, "w") as o:
-        o.write(f"# source: {path} (ncu --set full --clock-control none --import-source on)\n")
+        o.write(f"# source: {path} (ncu --set full --clock-control none)\n")
         for r in rows[2:]:
             o.write("----\n")
             for i in idx:

@@ -5,7 +5,7 @@ set -x
 mkdir -p gpurun_out
 NV='--nvtx --nvtx-include profile/'
 L='--metrics gpu__time_duration.sum --clock-control none --csv'
-F='--set full --clock-control none --import-source on'
+F='--set full --clock-control none'
 S='python tools/ncu_summary.py'
 ncu $NV $L --log-file gpurun_out/r02_cfg2_decode_launches.csv python tools/ncu_decode.py --workload cfg2 --steps 2 > gpurun_out/r02_p1.log 2>&1
 ncu $NV $L --log-file gpurun_out/r02_sq_decode_launches.csv python tools/ncu_decode.py --workload sq --steps 2 > gpurun_out/r02_p2.log 2>&1
@@ -23,7 +23,7 @@ ls -la gpurun_out/r02_*
 ncu $F -k regex:gemv_mma -s 8 -c 1 -o gpurun_out/mma4_w8m8_qkv python tools/gemv_mma_bench.py w8 8 qkv > gpurun_out/mma4_a.log 2>&1
 ncu $F -k regex:gemv_mma -s 8 -c 1 -o gpurun_out/mma4_w8m8_down python tools/gemv_mma_bench.py w8 8 down > gpurun_out/mma4_b.log 2>&1
 ncu $F -k regex:gemv_mma -s 8 -c 1 -o gpurun_out/mma4_w4m1_gu python tools/gemv_mma_bench.py w4 1 gate_up > gpurun_out/mma4_c.log 2>&1
-for r in w8m8_qkv w8m8_down w4m1_gu; do $S full gpurun_out/mma4_$r.ncu-rep gpurun_out/r02_gemv_mma_${r}_full.txt; python tools/ncu_hotspots.py gpurun_out/mma4_$r.ncu-rep >> gpurun_out/r02_gemv_mma_${r}_full.txt; done
+for r in w8m8_qkv w8m8_down w4m1_gu; do $S full gpurun_out/mma4_$r.ncu-rep gpurun_out/r02_gemv_mma_${r}_full.txt; done
 # launch lists of the tree with the new GEMV
 ncu $NV $L --log-file gpurun_out/r02b_cfg3_int8kv_decode_launches.csv python tools/ncu_decode.py --workload cfg3_int8kv --steps 2 > gpurun_out/r02_p8.log 2>&1
 ncu $NV $L --log-file gpurun_out/r02b_cfg5_decode_launches.csv python tools/ncu_decode.py --workload cfg5 --steps 2 > gpurun_out/r02_p9.log 2>&1
