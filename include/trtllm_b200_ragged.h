@@ -1,0 +1,103 @@
+/*
+ * trtllm_b200_ragged.h — C ABI of the operators that run a RAGGED in-flight batch: every call works on N token
+ * rows that belong to E sequences, each sequence bringing any number of new tokens (a portion of a prompt or one
+ * generated token) on top of what its pages of the cache pool and its state slot already hold.
+ *
+ * Conventions (as in trtllm_b200.h): device pointers, asynchronous on `stream`, 0 on success, negative for a
+ * rejected argument, positive cudaError_t.  Element types are named by TB_DT_*; "T" below is the model's storage
+ * type (bf16, or fp32 for the all-32-bit mode).  The residual stream, every normalisation, softmax, the recurrent
+ * state and everything that feeds a recurrence are fp32 in both modes.
+ *
+ * Batch description (device int32 arrays, built by the scheduler once per step):
+ *   tok_seq[N]   index of the row's sequence in this step        tok_pos[N]   position of the row in its sequence
+ *   seq_start[E] first row of the sequence                       seq_len[E]   rows it brings
+ *   seq_past[E]  positions it already holds (= tok_pos of its first row)
+ *   seq_slot[E]  its recurrent-state slot                        block_table[E, max_blocks] its pages of the pool
+ */
+#ifndef TRTLLM_B200_RAGGED_H
+#define TRTLLM_B200_RAGGED_H
+
+#include "trtllm_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { TB_DT_F32 = 1, TB_DT_BF16 = 2 };
+enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1 };
+/* tb_linear compute paths: AUTO = tensor cores for bf16 weights, FMA for fp32 weights; FMA32 = fp32 multiply-add in a
+ * fixed k order whatever the storage type (the all-32-bit mode, and the small products that feed a recurrence). */
+enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1 };
+
+/* C[b][m, n] = act( sum_k A[b][m, k] * W[b][n, k] + bias[b][n] ),  b < batch.
+ * A: a_dtype, row stride lda, batch stride a_bs (elements).  W: w_dtype, [N, K] rows contiguous, batch stride w_bs.
+ * bias: w_dtype or NULL, batch stride bias_bs.  C: c_dtype, row stride ldc, batch stride c_bs.
+ * The sum over k runs in the same order for every row, whatever M is and wherever the row stands in the batch. */
+int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const void* a, int a_dtype, int64_t lda, int64_t a_bs,
+              const void* w, int w_dtype, int64_t w_bs, const void* bias, int64_t bias_bs, int M, int N, int K, int batch,
+              int act, int compute, tb_stream_t stream);
+
+/* out[n, :] = table[ids[n], :] * scale  (fp32 residual stream; ids clamped into [0, vocab)). */
+int tb_embed_scaled(float* out, const void* table, int t_dtype, const int* ids, float scale, int rows, int width,
+                    int vocab, tb_stream_t stream);
+
+/* y = x / sqrt(mean(x^2) + eps) * (w + w_offset) over `cols` columns of each row; x fp32 with row stride ldi.
+ * accumulate != 0: out (fp32) += y — the residual update of a layer that normalises the sublayer's OUTPUT;
+ * else out = y in out_dtype.  w == NULL: no weight.  rows_idx != NULL: row r of out comes from row rows_idx[r] of x. */
+int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, int w_dtype,
+                    float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate, tb_stream_t stream);
+
+/* Gated feed-forward activation with clamps: g = min(gu[n, j], limit), u = clamp(gu[n, ff + j], -limit, limit),
+ * out[n, j] = g * sigmoid(alpha * g) * (u + up_shift).  limit <= 0: no clamp.  gu fp32 [rows, 2 ff]. */
+int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, float alpha, float limit, float up_shift,
+                 tb_stream_t stream);
+
+/* cos / sin of pos * base^(-2 i / dims), i < dims / 2, for every row: table fp32 [N, dims / 2, 2] (angles in fp64). */
+int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream);
+
+/* Rotated tail of the queries into the attention operand: for head h of row n the `rot_dim` elements of q (fp32,
+ * [N, H, dim + rot_dim]) behind the first `dim` are rotated pairwise (2i, 2i + 1) over their first `dims` elements by
+ * the row's table entry and stored as T at qa[n, h, lat + j], qa being [N, H, lat + rot_dim]. */
+int tb_rope_query_tail(void* qa, int dtype, const float* q, const float* table, int rows, int heads, int dim,
+                       int rot_dim, int dims, int lat, tb_stream_t stream);
+
+/* Latent KV append: row n of kv (fp32, stride ldkv) holds `lat` latent values and `rot_dim` shared rotary key
+ * values.  The latent is RMS-normalised (weight w, eps), the key part rotated by the row's table entry, and both are
+ * stored as one entry [lat + rot_dim] of type T at the row's position in its sequence's pages:
+ * pool[(block_table[seq, pos / page] * page + pos % page) * (lat + rot_dim)]. */
+int tb_latent_kv_append(void* pool, int dtype, const float* kv, int64_t ldkv, const void* w, int w_dtype, float eps,
+                        const float* table, int dims, const int* tok_seq, const int* tok_pos, const int* block_table,
+                        int max_blocks, int page, int rows, int lat, int rot_dim, tb_stream_t stream);
+
+/* Causal attention of every row over its sequence's cached latent entries 0..pos (multi-query form: one entry serves
+ * all heads).  qa T [N, H, lat + rot_dim]: per head the query absorbed into latent space, then its rotated tail.
+ * score = scale * <qa, entry>; softmax in fp32 over the visible entries; out T [N, H, lat] = sum_j p_j * entry_j[:lat].
+ * Keys are visited in blocks of 32 positions from 0, so a row's result does not depend on how its prompt was cut
+ * or on what else is in the batch. */
+int tb_latent_attention(void* out, const void* qa, const void* pool, int dtype, const int* tok_seq, const int* tok_pos,
+                        const int* block_table, int max_blocks, int page, int rows, int heads, int lat, int rot_dim,
+                        float scale, tb_stream_t stream);
+
+/* Per-channel causal convolution over a ragged batch with carried inputs: out[n, c] = bias[c] + sum_k w[c, k] *
+ * x(pos - (taps - 1 - k)), where positions before the sequence's portion come from state[slot] (fp32
+ * [slots, taps - 1, C], oldest first) and positions before the sequence's start are zero.  x, out fp32 [N, C]. */
+int tb_causal_conv1d(float* out, const float* x, const void* w, const void* bias, int w_dtype, const float* state,
+                     const int* tok_seq, const int* tok_pos, const int* seq_start, const int* seq_past,
+                     const int* seq_slot, int rows, int channels, int taps, tb_stream_t stream);
+/* state[slot] <- the last taps - 1 inputs of (what it held ++ this step's rows); run after tb_causal_conv1d. */
+int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, const int* seq_len, const int* seq_past,
+                            const int* seq_slot, int seqs, int channels, int taps, tb_stream_t stream);
+
+/* Real-gated linear recurrent unit over a ragged batch.  gates fp32 [N, blocks, 2, C / blocks]: per block the
+ * recurrence-gate logits, then the input-gate logits (biases already added).  Per channel, in sequence order:
+ *   r = sigmoid(gr), i = sigmoid(gi), log a = -c * r * softplus(lam), S <- exp(log a) * S + sqrt(1 - exp(2 log a)) * i * u
+ * with S read from / written to state[slot] (fp32 [slots, C]; zero at a sequence's first position), and
+ * out[n, ch] = S * y[n, ch] stored as T.  u fp32 [N, C], y T [N, C], lam w_dtype [C]. */
+int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, const void* lam, int w_dtype, const void* y,
+                  float* state, const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot,
+                  int seqs, int channels, int blocks, float c, tb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRTLLM_B200_RAGGED_H */

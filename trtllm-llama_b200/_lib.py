@@ -178,7 +178,29 @@ SIGNATURES.update({
     "tb_ar_allreduce": (i32, [vp, i32, vp, vp, i64, vp]),
 })
 
+# include/trtllm_b200_ragged.h: operators over a ragged in-flight batch (d = double for the rotary base)
+f64 = C.c_double
+RAGGED_SIGNATURES = {
+    "tb_linear": (i32, [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),
+    "tb_rmsnorm_rows": (i32, [vp, i32, i64, vp, i64, vp, i32, f32, f32, vp, i32, i32, i32, vp]),
+    "tb_gated_act": (i32, [vp, i32, vp, i32, i32, f32, f32, f32, vp]),
+    "tb_rope_table": (i32, [vp, vp, i32, i32, f64, vp]),
+    "tb_rope_query_tail": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_latent_kv_append": (i32, [vp, i32, vp, i64, vp, i32, f32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "tb_latent_attention": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "tb_causal_conv1d": (i32, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_causal_conv1d_update": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_rglru_scan": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]),
+}
+SIGNATURES.update(RAGGED_SIGNATURES)
+# what libtrtllm_b200_ragged.so exports (csrc/Makefile target `ragged`): the operators above plus the sampling, arg-max
+# and copy kernels a generation loop over them uses
+RAGGED_LIB_PATH = os.path.join(_HERE, "libtrtllm_b200_ragged.so")
+_RAGGED_ALSO = ("tb_version", "tb_check_device", "tb_argmax", "tb_sample", "tb_copy", "tb_fill_int")
+
 _lib = None
+_ragged = None
 
 
 def load_library(path: str | None = None):
@@ -200,9 +222,61 @@ def load_library(path: str | None = None):
     return h
 
 
+def _type(h, names):
+    for name in names:
+        res, args = SIGNATURES[name]
+        fn = getattr(h, name)
+        fn.restype = res
+        fn.argtypes = args
+    return h
+
+
+def build_library(target: str = "all"):
+    """``make <target>`` in csrc/ (``all``: the whole library; ``ragged``: the ragged-batch operator subset)."""
+    import subprocess
+    r = subprocess.run(["make", "-j", str(min(8, os.cpu_count() or 4)), target], cwd=os.path.join(_HERE, "csrc"),
+                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise LibraryNotBuilt(f"make {target} failed:\n{r.stdout[-4000:]}")
+
+
+def load_ragged_library(build: bool = False):
+    """The library that holds the ragged-batch operators: the full library when it is built (it contains them), else the
+    subset library, compiled on demand when ``build`` is set (a fresh checkout that only serves such a model)."""
+    global _ragged
+    if _ragged is not None:
+        return _ragged
+    if os.path.exists(LIB_PATH):
+        try:
+            _ragged = load_library()
+            return _ragged
+        except (AttributeError, OSError):      # an older build without these operators: fall through to the subset
+            pass
+    if not os.path.exists(RAGGED_LIB_PATH):
+        if not build:
+            raise LibraryNotBuilt(f"{RAGGED_LIB_PATH} not found: run `make ragged` in csrc/ (there is no CPU fallback)")
+        build_library("ragged")
+    _ragged = _type(C.CDLL(RAGGED_LIB_PATH, mode=C.RTLD_GLOBAL), list(RAGGED_SIGNATURES) + list(_RAGGED_ALSO))
+    return _ragged
+
+
+class _LazyRagged:
+    def __getattr__(self, name):
+        return getattr(load_ragged_library(), name)
+
+
+ragged_lib = _LazyRagged()
+
+
 class _Lazy:
     def __getattr__(self, name):
-        return getattr(load_library(), name)
+        try:
+            return getattr(load_library(), name)
+        except LibraryNotBuilt:
+            # a checkout that built only the ragged subset still has the sampling / arg-max / copy kernels
+            if _ragged is not None and (name in RAGGED_SIGNATURES or name in _RAGGED_ALSO):
+                return getattr(_ragged, name)
+            raise
 
 
 lib = _Lazy()

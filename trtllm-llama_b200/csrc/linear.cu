@@ -1,0 +1,245 @@
+// Dense projections of the ragged-batch models: C = act(A W^T + bias) with bf16 or fp32 storage and fp32 accumulation.
+//
+//   linear_mma_kernel   bf16 weights on tensor cores (mma.sync m16n8k16 bf16, fp32 accumulators); A may arrive as fp32
+//                       (the residual stream) and is rounded to bf16 while it is staged in shared memory, so no separate
+//                       cast pass runs in front of a projection.  64 x 64 x 32 tiles, 4 warps of 32 x 32.
+//   linear_fma_kernel   fp32 multiply-add with every product taken in fp32 (no TF32, no split-K): the all-32-bit mode and
+//                       the small block-diagonal products that feed a recurrence.  64 x 64 x 16 tiles, 4 x 4 per thread.
+//
+// Both walk k in one fixed order per output element, so a token's result is the same wherever it stands in a batch.
+// blockIdx.z walks a batch of independent problems (per-head absorbed projections, block-diagonal gates).
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "../../include/trtllm_b200_ragged.h"
+
+namespace tb {
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+struct LinArgs {
+  void* c; const void* a; const void* w; const void* bias;
+  int64_t ldc, c_bs, lda, a_bs, w_bs, bias_bs;
+  int M, N, K, act;
+};
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename AT, typename WT, typename CT>
+__global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  const int b = blockIdx.z;
+  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
+  const WT* W = reinterpret_cast<const WT*>(p.w) + (int64_t) b * p.w_bs;
+  CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;      // thread -> 4 rows (ty) x 4 cols (tx)
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < p.K; k0 += BK) {
+    // 64 x 16 elements per operand, 256 threads: 4 each; k fastest so global reads run along the rows
+    for (int e = threadIdx.x; e < BM * BK; e += 256) {
+      const int r = e / BK, k = e % BK;
+      const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
+      As[k][r] = (gm < p.M && gk < p.K) ? to_f<AT>(A[(int64_t) gm * p.lda + gk]) : 0.f;
+      Ws[k][r] = (gn < p.N && gk < p.K) ? to_f<WT>(W[(int64_t) gn * p.K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  const WT* bias = p.bias ? reinterpret_cast<const WT*>(p.bias) + (int64_t) b * p.bias_bs : nullptr;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= p.N) continue;
+      float v = acc[i][j];
+      if (bias) v += to_f<WT>(bias[gn]);
+      if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+      C[(int64_t) gm * p.ldc + gn] = from_f<CT>(v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename AT, typename CT>
+__global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, int vec_w) {
+  constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;       // 80-byte rows: fragment reads hit 32 distinct banks
+  __shared__ __align__(16) __nv_bfloat16 As[BM][LD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[BN][LD];
+  const int b = blockIdx.z;
+  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) b * p.w_bs;
+  CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int wm = (warp / 2) * 32, wn = (warp % 2) * 32;
+  const int g = lane / 4, t = lane % 4;
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+
+  for (int k0 = 0; k0 < p.K; k0 += BK) {
+    // stage A: 64 rows x 32 k = 256 groups of 8 elements, 2 per thread
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int e = threadIdx.x + it * 128;
+      const int r = e / 4, kc = (e % 4) * 8;
+      const int gm = m0 + r, gk = k0 + kc;
+      __align__(16) __nv_bfloat16 v[8];
+      if (gm < p.M && vec_a && gk + 8 <= p.K) {
+        const AT* src = A + (int64_t) gm * p.lda + gk;
+        if constexpr (sizeof(AT) == 4) {
+          const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
+          v[0] = __float2bfloat16_rn(f0.x); v[1] = __float2bfloat16_rn(f0.y); v[2] = __float2bfloat16_rn(f0.z);
+          v[3] = __float2bfloat16_rn(f0.w); v[4] = __float2bfloat16_rn(f1.x); v[5] = __float2bfloat16_rn(f1.y);
+          v[6] = __float2bfloat16_rn(f1.z); v[7] = __float2bfloat16_rn(f1.w);
+        } else {
+          *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (gm < p.M && gk + j < p.K) ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) gm * p.lda + gk + j]))
+                                            : __float2bfloat16_rn(0.f);
+      }
+      *reinterpret_cast<uint4*>(&As[r][kc]) = *reinterpret_cast<const uint4*>(v);
+    }
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int e = threadIdx.x + it * 128;
+      const int r = e / 4, kc = (e % 4) * 8;
+      const int gn = n0 + r, gk = k0 + kc;
+      __align__(16) __nv_bfloat16 v[8];
+      if (gn < p.N && vec_w && gk + 8 <= p.K) {
+        *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(W + (int64_t) gn * p.K + gk);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          v[j] = (gn < p.N && gk + j < p.K) ? W[(int64_t) gn * p.K + gk + j] : __float2bfloat16_rn(0.f);
+      }
+      *reinterpret_cast<uint4*>(&Ws[r][kc]) = *reinterpret_cast<const uint4*>(v);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      uint32_t af[2][4], bf[4][2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = wm + i * 16 + g;
+        af[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * t]);
+        af[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * t]);
+        af[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][kk + 2 * t + 8]);
+        af[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = wn + j * 8 + g;
+        bf[j][0] = *reinterpret_cast<const uint32_t*>(&Ws[c][kk + 2 * t]);
+        bf[j][1] = *reinterpret_cast<const uint32_t*>(&Ws[c][kk + 2 * t + 8]);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j]);
+    }
+    __syncthreads();
+  }
+  const __nv_bfloat16* bias = p.bias ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + (int64_t) b * p.bias_bs : nullptr;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int gm = m0 + wm + i * 16 + g + (k >= 2 ? 8 : 0);
+        const int gn = n0 + wn + j * 8 + 2 * t + (k & 1);
+        if (gm >= p.M || gn >= p.N) continue;
+        float v = acc[i][j][k];
+        if (bias) v += __bfloat162float(bias[gn]);
+        if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+        C[(int64_t) gm * p.ldc + gn] = from_f<CT>(v);
+      }
+}
+
+template <typename AT, typename WT>
+int launch_fma(const LinArgs& p, int c_dtype, dim3 grid, cudaStream_t s) {
+  if (c_dtype == TB_DT_F32) linear_fma_kernel<AT, WT, float><<<grid, 256, 0, s>>>(p);
+  else linear_fma_kernel<AT, WT, __nv_bfloat16><<<grid, 256, 0, s>>>(p);
+  return 0;
+}
+
+}  // namespace
+}  // namespace tb
+
+extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const void* a, int a_dtype, int64_t lda,
+                         int64_t a_bs, const void* w, int w_dtype, int64_t w_bs, const void* bias, int64_t bias_bs, int M,
+                         int N, int K, int batch, int act, int compute, tb_stream_t stream) {
+  using namespace tb;
+  auto ok = [](int d) { return d == TB_DT_F32 || d == TB_DT_BF16; };
+  if (!c || !a || !w || !ok(c_dtype) || !ok(a_dtype) || !ok(w_dtype) || N <= 0 || K <= 0 || batch <= 0 || M < 0) return -1;
+  if (M == 0) return 0;
+  if (batch > 65535 || (M + 63) / 64 > 65535) return -2;
+  LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+  if (w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO) {
+    const int asz = a_dtype == TB_DT_F32 ? 4 : 2;
+    const int vec_a = ((uintptr_t) a % 16 == 0) && (lda * asz % 16 == 0) && (a_bs * asz % 16 == 0);
+    const int vec_w = ((uintptr_t) w % 16 == 0) && (K % 8 == 0) && (w_bs % 8 == 0);
+    if (a_dtype == TB_DT_F32) {
+      if (c_dtype == TB_DT_F32) linear_mma_kernel<float, float><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+      else linear_mma_kernel<float, __nv_bfloat16><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+    } else {
+      if (c_dtype == TB_DT_F32) linear_mma_kernel<__nv_bfloat16, float><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+      else linear_mma_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+    }
+  } else if (w_dtype == TB_DT_BF16) {
+    if (a_dtype == TB_DT_F32) launch_fma<float, __nv_bfloat16>(p, c_dtype, grid, s);
+    else launch_fma<__nv_bfloat16, __nv_bfloat16>(p, c_dtype, grid, s);
+  } else {
+    if (a_dtype == TB_DT_F32) launch_fma<float, float>(p, c_dtype, grid, s);
+    else launch_fma<__nv_bfloat16, float>(p, c_dtype, grid, s);
+  }
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,162 @@
+// Row-wise kernels of the ragged-batch models whose residual stream is fp32: scaled embedding, RMS normalisation of a
+// sublayer's output accumulated into the residual, the clamped gated activation of the feed-forward, and the rotary
+// table.  All are bandwidth-bound passes over [rows, width]; statistics and sums are fp32.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "../../include/trtllm_b200_ragged.h"
+
+namespace tb {
+namespace {
+
+__device__ __forceinline__ float ld_f(const void* p, int dtype, int64_t i) {
+  return dtype == TB_DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void st_f(void* p, int dtype, int64_t i, float v) {
+  if (dtype == TB_DT_F32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+__global__ void embed_scaled_kernel(float* out, const void* table, int t_dtype, const int* ids, float scale, int width,
+                                    int vocab) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  for (int c = threadIdx.x; c < width; c += blockDim.x)
+    out[(int64_t) row * width + c] = ld_f(table, t_dtype, (int64_t) id * width + c) * scale;
+}
+
+// one CTA per row; the sum of squares is reduced in a fixed tree (warp shuffles, then warp 0 over the warp sums)
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi,
+                                                           const void* w, int w_dtype, float w_offset, float eps,
+                                                           const int* rows_idx, int cols, int accumulate) {
+  __shared__ float red[8];
+  __shared__ float inv_s;
+  const int row = blockIdx.x;
+  const float* xr = x + (int64_t) (rows_idx ? rows_idx[row] : row) * ldi;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float v = xr[c]; ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) inv_s = 1.f / sqrtf(v / (float) cols + eps);
+  }
+  __syncthreads();
+  const float inv = inv_s;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float y = xr[c] * inv;
+    if (w) y *= ld_f(w, w_dtype, c) + w_offset;
+    const int64_t o = (int64_t) row * ldo + c;
+    if (accumulate) reinterpret_cast<float*>(out)[o] += y;
+    else st_f(out, out_dtype, o, y);
+  }
+}
+
+__global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int64_t n, int ff, float alpha, float limit,
+                                 float up_shift) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+    const int64_t row = i / ff;
+    const int j = (int) (i % ff);
+    float g = gu[row * 2 * ff + j], u = gu[row * 2 * ff + ff + j];
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    const float sg = 1.f / (1.f + expf(-alpha * g));
+    st_f(out, out_dtype, i, g * sg * (u + up_shift));
+  }
+}
+
+__global__ void rope_table_kernel(float* table, const int* tok_pos, int rows, int half, int dims, double base) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * half) return;
+  const int row = i / half, f = i % half;
+  const double freq = pow(base, -2.0 * (double) f / (double) dims);
+  double s, c;
+  sincos((double) tok_pos[row] * freq, &s, &c);
+  table[2 * (int64_t) i] = (float) c;
+  table[2 * (int64_t) i + 1] = (float) s;
+}
+
+__global__ void rope_query_tail_kernel(void* qa, int dtype, const float* q, const float* table, int rows, int heads, int dim,
+                                       int rot_dim, int dims, int lat) {
+  // one thread per (row, head, pair-or-passthrough element)
+  const int per = rot_dim - dims / 2;            // dims/2 pairs + (rot_dim - dims) unrotated elements
+  const int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x;
+  if (i >= (int64_t) rows * heads * per) return;
+  const int e = (int) (i % per);
+  const int64_t rh = i / per;
+  const int row = (int) (rh / heads);
+  const float* src = q + rh * (dim + rot_dim) + dim;
+  const int64_t dst = rh * (lat + rot_dim) + lat;
+  if (e < dims / 2) {
+    const float c = table[((int64_t) row * (dims / 2) + e) * 2], s = table[((int64_t) row * (dims / 2) + e) * 2 + 1];
+    const float u = src[2 * e], v = src[2 * e + 1];
+    st_f(qa, dtype, dst + 2 * e, u * c - v * s);
+    st_f(qa, dtype, dst + 2 * e + 1, v * c + u * s);
+  } else {
+    const int j = dims + (e - dims / 2);
+    st_f(qa, dtype, dst + j, src[j]);
+  }
+}
+
+}  // namespace
+}  // namespace tb
+
+using namespace tb;
+static inline bool dt_ok(int d) { return d == TB_DT_F32 || d == TB_DT_BF16; }
+
+extern "C" int tb_embed_scaled(float* out, const void* table, int t_dtype, const int* ids, float scale, int rows, int width,
+                               int vocab, tb_stream_t stream) {
+  if (!out || !table || !ids || !dt_ok(t_dtype) || width <= 0 || vocab <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  embed_scaled_kernel<<<rows, 128, 0, (cudaStream_t) stream>>>(out, table, t_dtype, ids, scale, width, vocab);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, int w_dtype,
+                               float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate,
+                               tb_stream_t stream) {
+  if (!out || !x || !dt_ok(out_dtype) || (w && !dt_ok(w_dtype)) || cols <= 0 || rows < 0) return -1;
+  if (accumulate && out_dtype != TB_DT_F32) return -2;
+  if (rows == 0) return 0;
+  rmsnorm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, ldo, x, ldi, w, w_dtype, w_offset, eps,
+                                                               rows_idx, cols, accumulate);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, float alpha, float limit,
+                            float up_shift, tb_stream_t stream) {
+  if (!out || !gu || !dt_ok(out_dtype) || ff <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * ff;
+  const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  gated_act_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, gu, n, ff, alpha, limit, up_shift);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream) {
+  if (!table || !tok_pos || dims <= 0 || dims % 2 || rows < 0 || !(base > 0.0)) return -1;
+  if (rows == 0) return 0;
+  const int n = rows * (dims / 2);
+  rope_table_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(table, tok_pos, rows, dims / 2, dims, base);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_rope_query_tail(void* qa, int dtype, const float* q, const float* table, int rows, int heads, int dim,
+                                  int rot_dim, int dims, int lat, tb_stream_t stream) {
+  if (!qa || !q || !table || !dt_ok(dtype) || heads <= 0 || dim < 0 || rot_dim <= 0 || dims <= 0 || dims % 2 ||
+      dims > rot_dim || lat < 0 || rows < 0)
+    return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * heads * (rot_dim - dims / 2);
+  rope_query_tail_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, (cudaStream_t) stream>>>(qa, dtype, q, table, rows, heads,
+                                                                                           dim, rot_dim, dims, lat);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

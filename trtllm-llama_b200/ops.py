@@ -334,3 +334,152 @@ def gemm_tc_swiglu(kind, x, w_gate_up, *, sc=None, sr=None):
     check(lib.tb_gemm_tc_swiglu(kind, _p(c), _p(x), _p(w_gate_up), _p(sc), _p(sr), int(sc is not None and sc.numel() > 1),
                                 int(sr is not None and sr.numel() > 1), M, N, K, _stream()), "tb_gemm_tc_swiglu")
     return c
+
+
+# ------------------------------------------------------------------------------------------------
+# operators over a ragged in-flight batch (include/trtllm_b200_ragged.h).  They are served by whichever
+# library holds them (the full one, or the ragged subset), so a model that needs only these does not need the rest.
+# ------------------------------------------------------------------------------------------------
+from ._lib import ragged_lib as _rl  # noqa: E402
+
+DT_F32, DT_BF16 = 1, 2
+ACT_NONE, ACT_GELU_TANH = 0, 1
+COMPUTE_AUTO, COMPUTE_FMA32 = 0, 1
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return DT_F32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise TypeError(f"ragged operators take float32 or bfloat16 tensors, not {t.dtype}")
+
+
+def _chk_dev(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("expected CUDA tensors (there is no CPU path)")
+
+
+def linear(a, w, bias=None, out=None, out_dtype=None, act=ACT_NONE, compute=COMPUTE_AUTO):
+    """out[b][m, n] = act(sum_k a[b][m, k] w[b][n, k] + bias[b][n]).
+
+    ``w`` is [N, K] or, for a batch of independent products, [B, N, K]; ``a`` is then a [M, B, K] view (any row
+    stride, unit stride on k) and ``out`` a [M, B, N] view of the caller's buffer.  Unbatched: a [M, K], out [M, N]."""
+    _chk_dev(a, w, bias, out)
+    batched = w.dim() == 3
+    if not w.is_contiguous() or (bias is not None and not bias.is_contiguous()):
+        raise ValueError("weights and biases must be contiguous")
+    if batched:
+        B, N, K = w.shape
+        M = a.shape[0]
+        if out is None:
+            out = torch.empty((M, B, N), dtype=out_dtype or a.dtype, device=a.device)
+        if a.shape != (M, B, K) or out.shape != (M, B, N) or a.stride(2) != 1 or out.stride(2) != 1:
+            raise ValueError("batched linear: a [M, B, K], out [M, B, N] with unit inner stride")
+        lda, a_bs, ldc, c_bs = a.stride(0), a.stride(1), out.stride(0), out.stride(1)
+        w_bs, b_bs = N * K, N
+    else:
+        (N, K), B = w.shape, 1
+        M = a.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+        if a.shape != (M, K) or out.shape != (M, N) or a.stride(1) != 1 or out.stride(1) != 1:
+            raise ValueError("linear: a [M, K], out [M, N] with unit inner stride")
+        lda, a_bs, ldc, c_bs, w_bs, b_bs = a.stride(0), 0, out.stride(0), 0, 0, 0
+    if bias is not None and bias.dtype != w.dtype:
+        raise TypeError("bias must have the weight's type")
+    check(_rl.tb_linear(_p(out), _dt(out), ldc, c_bs, _p(a), _dt(a), lda, a_bs, _p(w), _dt(w), w_bs, _p(bias), b_bs,
+                        M, N, K, B, act, compute, _stream()), "tb_linear")
+    return out
+
+
+def embed_scaled(table, ids, scale):
+    _chk_dev(table, ids)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    check(_rl.tb_embed_scaled(_p(out), _p(table), _dt(table), _p(ids), float(scale), ids.numel(), table.shape[1],
+                              table.shape[0], _stream()), "tb_embed_scaled")
+    return out
+
+
+def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=False, rows_idx=None, cols=None):
+    """RMS norm of fp32 rows (``cols`` leading columns of each); accumulate=True adds the result into fp32 ``out``."""
+    _chk_dev(x, w, out, rows_idx)
+    cols = x.shape[1] if cols is None else cols
+    rows = x.shape[0] if rows_idx is None else rows_idx.numel()
+    if x.dtype != torch.float32 or x.stride(1) != 1:
+        raise ValueError("rmsnorm_rows normalises fp32 rows")
+    if out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype or torch.float32, device=x.device)
+    check(_rl.tb_rmsnorm_rows(_p(out), _dt(out), out.stride(0), _p(x), x.stride(0), _p(w), _dt(w) if w is not None else 0,
+                              float(w_offset), float(eps), _p(rows_idx), rows, cols, int(accumulate), _stream()),
+          "tb_rmsnorm_rows")
+    return out
+
+
+def gated_act(gu, out_dtype, alpha, limit, up_shift):
+    _chk_cuda(gu)
+    rows, ff = gu.shape[0], gu.shape[1] // 2
+    out = torch.empty((rows, ff), dtype=out_dtype, device=gu.device)
+    check(_rl.tb_gated_act(_p(out), _dt(out), _p(gu), rows, ff, float(alpha), float(limit), float(up_shift), _stream()),
+          "tb_gated_act")
+    return out
+
+
+def rope_table(tok_pos, dims, base):
+    _chk_dev(tok_pos)
+    out = torch.empty((tok_pos.numel(), dims // 2, 2), dtype=torch.float32, device=tok_pos.device)
+    check(_rl.tb_rope_table(_p(out), _p(tok_pos), tok_pos.numel(), dims, float(base), _stream()), "tb_rope_table")
+    return out
+
+
+def rope_query_tail(qa, q, table, heads, dim, rot_dim, dims, lat):
+    _chk_cuda(qa, q, table)
+    check(_rl.tb_rope_query_tail(_p(qa), _dt(qa), _p(q), _p(table), q.shape[0], heads, dim, rot_dim, dims, lat, _stream()),
+          "tb_rope_query_tail")
+
+
+def latent_kv_append(pool, kv, w, eps, table, dims, batch, page, lat, rot_dim):
+    _chk_cuda(pool, kv, w, table)
+    check(_rl.tb_latent_kv_append(_p(pool), _dt(pool), _p(kv), kv.stride(0), _p(w), _dt(w), float(eps), _p(table), dims,
+                                  _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.block_table), batch.max_blocks, page,
+                                  kv.shape[0], lat, rot_dim, _stream()), "tb_latent_kv_append")
+
+
+def latent_attention(qa, pool, batch, page, heads, lat, rot_dim, scale):
+    _chk_cuda(qa, pool)
+    out = torch.empty((qa.shape[0], heads, lat), dtype=qa.dtype, device=qa.device)
+    check(_rl.tb_latent_attention(_p(out), _p(qa), _p(pool), _dt(pool), _p(batch.tok_seq), _p(batch.tok_pos),
+                                  _p(batch.block_table), batch.max_blocks, page, qa.shape[0], heads, lat, rot_dim,
+                                  float(scale), _stream()), "tb_latent_attention")
+    return out
+
+
+def causal_conv1d(x, w, bias, state, batch):
+    """Ragged per-channel causal convolution; then the carried inputs in ``state`` move on by this step's rows."""
+    _chk_cuda(x, w, bias, state)
+    rows, ch = x.shape
+    taps = w.shape[1]
+    out = torch.empty_like(x)
+    check(_rl.tb_causal_conv1d(_p(out), _p(x), _p(w), _p(bias), _dt(w), _p(state), _p(batch.tok_seq), _p(batch.tok_pos),
+                               _p(batch.seq_start), _p(batch.seq_past), _p(batch.seq_slot), rows, ch, taps, _stream()),
+          "tb_causal_conv1d")
+    check(_rl.tb_causal_conv1d_update(_p(state), _p(x), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
+                                      _p(batch.seq_slot), batch.num_seqs, ch, taps, _stream()), "tb_causal_conv1d_update")
+    return out
+
+
+def rglru_scan(u, gates, lam, y, state, batch, blocks, c):
+    _chk_cuda(u, gates, lam, y, state)
+    out = torch.empty_like(y)
+    check(_rl.tb_rglru_scan(_p(out), _dt(out), _p(u), _p(gates), _p(lam), _dt(lam), _p(y), _p(state), _p(batch.seq_start),
+                            _p(batch.seq_len), _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, u.shape[1], blocks,
+                            float(c), _stream()), "tb_rglru_scan")
+    return out
+
+
+def argmax_rows(logits):
+    _chk_cuda(logits)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    check(_rl.tb_argmax(_p(out), _p(logits), logits.shape[0], logits.shape[1], logits.stride(0), _stream()), "tb_argmax")
+    return out

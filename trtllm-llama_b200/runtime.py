@@ -460,6 +460,29 @@ class KVCacheManager:
             s.batch_idx = i
         return changed
 
+    # in-flight batching: sequences come, grow by any number of positions per step, and go, independently of one another
+    def reserve(self, sequence: GenerationSequence, total_len: int) -> bool:
+        """Make ``sequence`` own enough blocks for ``total_len`` positions (admitting it if it is new).  Returns True
+        when blocks were added.  Raises, leaving the sequence as it was, when the pool cannot cover it."""
+        have = self.allocated.get(sequence)
+        need = -(-total_len // self.tokens_per_block) - (len(have) if have is not None else 0)
+        if need <= 0 and have is not None:
+            return False
+        if need > len(self.free_blocks) or (len(have) if have else 0) + need > self.max_blocks_per_seq:
+            raise RuntimeError("Can't allocate new block for KV cache")
+        if have is None:
+            have = self.allocated[sequence] = []
+        for _ in range(need):
+            have.append(self.free_blocks.pop(0))
+        return need > 0
+
+    def release(self, sequence: GenerationSequence):
+        """A finished sequence hands its blocks back; the next sequence admitted may get them."""
+        self.free_blocks.extend(self.allocated.pop(sequence))
+
+    def blocks_of(self, sequence: GenerationSequence):
+        return self.allocated[sequence]
+
     def get_block_table(self, batch: int) -> torch.Tensor:
         t = torch.full((batch, self.max_blocks_per_seq), -1, dtype=torch.int32)
         for seq, ids in self.allocated.items():
