@@ -37,6 +37,15 @@ int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const void* a, in
               const void* w, int w_dtype, int64_t w_bs, const void* bias, int64_t bias_bs, int M, int N, int K, int batch,
               int act, int compute, tb_stream_t stream);
 
+/* Prompt-sized products of bf16 operands on the 5th-generation tensor cores (tcgen05 / TMEM / TMA, the kernel of
+ * tb_gemm_tc with bf16 formats): c = act(x w^T + bias); x [M, K], w [N, K] bf16 contiguous, 8 | K, both 16-byte aligned;
+ * c [M, N] contiguous fp32 (out_type 1) or bf16 (out_type 3); bias bf16 [N] or NULL; act TB_ACT_*.
+ * workspace / counters as for tb_gemm_tc (used only when M <= 16 splits K). */
+int tb_gemm_tc_bf16(void* c, int out_type, const void* x, const void* w, const void* bias, int act, int M, int N, int K,
+                    void* workspace, size_t workspace_bytes, int* counters, tb_stream_t stream);
+/* out bf16 [rows, cols] contiguous = x fp32 (row stride ld): the residual stream as a tensor-core operand. */
+int tb_cast_rows_bf16(void* out, const float* x, int64_t ld, int rows, int cols, tb_stream_t stream);
+
 /* out[n, :] = table[ids[n], :] * scale  (fp32 residual stream; ids clamped into [0, vocab)). */
 int tb_embed_scaled(float* out, const void* table, int t_dtype, const int* ids, float scale, int rows, int width,
                     int vocab, tb_stream_t stream);
@@ -73,10 +82,15 @@ int tb_latent_kv_append(void* pool, int dtype, const float* kv, int64_t ldkv, co
  * all heads).  qa T [N, H, lat + rot_dim]: per head the query absorbed into latent space, then its rotated tail.
  * score = scale * <qa, entry>; softmax in fp32 over the visible entries; out T [N, H, lat] = sum_j p_j * entry_j[:lat].
  * Keys are visited in blocks of 32 positions from 0, so a row's result does not depend on how its prompt was cut
- * or on what else is in the batch. */
+ * or on what else is in the batch.
+ * bf16 with 32 | lat, 16 | rot_dim runs on tensor cores (tb_latent_attention_tensor_cores tells): one CTA per (row,
+ * 16 heads, key range).  nsplit > 1 deals every row's key blocks to nsplit CTAs whose partial results (workspace: fp32
+ * [rows, heads, nsplit, lat + 2]) a second kernel merges — for steps with few rows and long contexts; other
+ * configurations ignore it. */
+int tb_latent_attention_tensor_cores(int dtype, int lat, int rot_dim);
 int tb_latent_attention(void* out, const void* qa, const void* pool, int dtype, const int* tok_seq, const int* tok_pos,
                         const int* block_table, int max_blocks, int page, int rows, int heads, int lat, int rot_dim,
-                        float scale, tb_stream_t stream);
+                        float scale, int nsplit, float* workspace, tb_stream_t stream);
 
 /* Per-channel causal convolution over a ragged batch with carried inputs: out[n, c] = bias[c] + sum_k w[c, k] *
  * x(pos - (taps - 1 - k)), where positions before the sequence's portion come from state[slot] (fp32
@@ -92,10 +106,12 @@ int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, 
  * recurrence-gate logits, then the input-gate logits (biases already added).  Per channel, in sequence order:
  *   r = sigmoid(gr), i = sigmoid(gi), log a = -c * r * softplus(lam), S <- exp(log a) * S + sqrt(1 - exp(2 log a)) * i * u
  * with S read from / written to state[slot] (fp32 [slots, C]; zero at a sequence's first position), and
- * out[n, ch] = S * y[n, ch] stored as T.  u fp32 [N, C], y T [N, C], lam w_dtype [C]. */
+ * out[n, ch] = S * y[n, ch] stored as T.  u fp32 [N, C], y T [N, C], lam w_dtype [C].
+ * max_len: the longest seq_len (host); with workspace (fp32, 3 * seqs * ceil(max_len / 64) * C) and max_len > 64 the rows
+ * of a sequence are scanned in parallel chunks of 64 whose summaries are carried in order. */
 int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, const void* lam, int w_dtype, const void* y,
                   float* state, const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot,
-                  int seqs, int channels, int blocks, float c, tb_stream_t stream);
+                  int seqs, int channels, int blocks, float c, int max_len, float* workspace, tb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -182,16 +182,19 @@ SIGNATURES.update({
 f64 = C.c_double
 RAGGED_SIGNATURES = {
     "tb_linear": (i32, [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_gemm_tc_bf16": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp]),
+    "tb_cast_rows_bf16": (i32, [vp, vp, i64, i32, i32, vp]),
     "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),
     "tb_rmsnorm_rows": (i32, [vp, i32, i64, vp, i64, vp, i32, f32, f32, vp, i32, i32, i32, vp]),
     "tb_gated_act": (i32, [vp, i32, vp, i32, i32, f32, f32, f32, vp]),
     "tb_rope_table": (i32, [vp, vp, i32, i32, f64, vp]),
     "tb_rope_query_tail": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "tb_latent_kv_append": (i32, [vp, i32, vp, i64, vp, i32, f32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
-    "tb_latent_attention": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "tb_latent_attention": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, vp]),
+    "tb_latent_attention_tensor_cores": (i32, [i32, i32, i32]),
     "tb_causal_conv1d": (i32, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
     "tb_causal_conv1d_update": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
-    "tb_rglru_scan": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, vp]),
+    "tb_rglru_scan": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp, vp]),
 }
 SIGNATURES.update(RAGGED_SIGNATURES)
 # what libtrtllm_b200_ragged.so exports (csrc/Makefile target `ragged`): the operators above plus the sampling, arg-max

@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <algorithm>
 #include <cstdlib>
+#include <cuda_bf16.h>
 #include "common.cuh"
 #include "kernels.h"
 #include "tmap_host.h"
@@ -36,7 +37,10 @@ enum { kGF16 = 0, kGW8 = 1, kGW4 = 2, kGI8 = 3 };   // same numbering as tb_gemv
 
 struct GemmTcParams {
   void* c;                 // [M, N] fp16 / fp32 / int32
-  int out_type;            // 0 fp16, 1 fp32, 2 int32
+  int out_type;            // 0 fp16, 1 fp32, 2 int32, 3 bf16
+  int bf16;                // KIND 0 only: operands are bf16 (same kind::f16 MMA, bf16 formats in the instruction descriptor)
+  const void* bias;        // bf16 operands only: optional bf16 [N], added before the activation
+  int act;                 // bf16 operands only: 0 none, 1 tanh-GELU
   const __half* residual;  // optional [M, N] (fp16 out only)
   const __half* w_scale;   // KIND 2/3: [N] fp16
   const float* sc;         // KIND 1: per-channel [N] or [1]
@@ -161,7 +165,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
   } else if (warp == 1) {
     // =========================== MMA issuer =============================
     if (lane == 0) {
-      constexpr uint32_t idesc = KIND == kGI8 ? kIdescI8(kTileN, NT) : kIdescF16(kTileN, NT);
+      const uint32_t idesc = KIND == kGI8 ? kIdescI8(kTileN, NT)
+                                          : (p.bf16 ? umma_idesc(1u /*F32*/, 1u /*BF16*/, kTileN, NT) : kIdescF16(kTileN, NT));
       int stage = 0, phase = 0, acc = 0, acc_phase = 0;
       for (int it = blockIdx.x; it < items; it += gridDim.x) {
         const int split = it % p.splits;
@@ -208,8 +213,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (Cfg::kWO || f16_scaled) chan = __half2float(p.w_scale[n]);
         if constexpr (KIND == kGI8) chan = p.sc[p.sc_per_channel ? n : 0];
       }
+      float bias_n = 0.f;
+      if (KIND == kGF16 && p.bias && n < p.N) bias_n = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[n]);
       auto finish = [&](float v, int m) {   // v: accumulated value as float, before scaling
         if (n >= p.N || m >= p.M) return;
+        if (KIND == kGF16 && p.bf16) {
+          v += bias_n;
+          if (p.act == 1) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+          const size_t o = (size_t) m * p.N + n;
+          if (p.out_type == 3) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
+          else reinterpret_cast<float*>(p.c)[o] = v;
+          return;
+        }
         if constexpr (KIND == kGI8) v = v * (chan * p.sr[p.sr_per_token ? m : 0]);
         if (Cfg::kWO || f16_scaled) v = v * chan;
         const size_t oi = (size_t) m * p.N + n;
@@ -385,9 +400,10 @@ static int launch_gemm_tc(GemmTcParams p, const void* x, const void* w, void* wo
   CUtensorMap tw, tx;
   int rc;
   if constexpr (KIND == kGF16) {
-    rc = make_tmap(&tw, w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.N, p.K, kTileN, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    const CUtensorMapDataType dt16 = p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    rc = make_tmap(&tw, w, dt16, 2, p.N, p.K, kTileN, 64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    rc = make_tmap(&tx, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.M, p.K, NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tmap(&tx, x, dt16, 2, p.M, p.K, NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   } else if constexpr (KIND == kGI8) {
     rc = make_tmap(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, p.N, p.K, kTileN, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
@@ -575,6 +591,20 @@ int tb_gemm_tc(int kind, void* c, int out_type, const void* x, const void* w, co
   }
   return -1;
 }
+}
+
+// bf16 operands through the same tcgen05 kernel (kind::f16 with bf16 formats): c = act(x w^T + bias), x [M, K] and w [N, K]
+// bf16 with K a multiple of 8, c [M, N] fp32 (out_type 1) or bf16 (3), bias bf16 [N] or NULL, act 0 | 1 (tanh-GELU).
+// Used by the ragged-batch models for prompt-sized row counts; workspace / counters as tb_gemm_tc (split-K at <= 16 rows).
+extern "C" int tb_gemm_tc_bf16(void* c, int out_type, const void* x, const void* w, const void* bias, int act, int M, int N,
+                               int K, void* workspace, size_t workspace_bytes, int* counters, cudaStream_t stream) {
+  using namespace tb;
+  if (!c || !x || !w || M < 1 || N < 1 || K < 8 || K % 8 || (out_type != 1 && out_type != 3) || act < 0 || act > 1) return -1;
+  if ((uintptr_t) x % 16 || (uintptr_t) w % 16) return -1;
+  GemmTcParams p{};
+  p.c = c; p.out_type = out_type; p.bf16 = 1; p.bias = bias; p.act = act;
+  p.M = M; p.N = N; p.K = K;
+  return dispatch_nt<kGF16>(p, x, w, workspace, workspace_bytes, counters, 0, 0, stream);
 }
 
 // Gate / up projection with SwiGLU in the tcgen05 epilogue (prefill shapes): w holds [N = 2 * inter, K] (gate rows, then up

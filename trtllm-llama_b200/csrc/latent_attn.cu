@@ -109,11 +109,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) latent_attention_kernel(T* ou
     const float corr = expf(m - m_new);               // 0 on the first tile (m = -inf)
     l = l * corr + warp_sum(p);
     m = m_new;
-    for (int c = lane; c < lat; c += 32) {
+    for (int c0 = 0; c0 < lat; c0 += 32) {            // every lane takes every trip: the shuffles below need the whole warp
+      const int c = c0 + lane < lat ? c0 + lane : lat - 1;
       float a = acc[c] * corr;
 #pragma unroll 8
       for (int jj = 0; jj < kKeyTile; ++jj) a = fmaf(__shfl_sync(0xffffffffu, p, jj), keys[jj * LDK + c], a);
-      acc[c] = a;
+      __syncwarp();
+      if (c0 + lane < lat) acc[c] = a;
+      __syncwarp();
     }
   }
   if (live) {
@@ -121,6 +124,225 @@ __global__ void __launch_bounds__(kAttnWarps * 32) latent_attention_kernel(T* ou
     T* dst = out + ((int64_t) row * heads + head) * lat;
     for (int c = lane; c < lat; c += 32) dst[c] = from_f<T>(acc[c] * inv);
   }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core form (bf16 storage): one CTA = one query row x 16 heads (the MMA's M) x one range of key tiles.
+//   S [16 x 32]  = Q [16 x D] . K^T          warp w owns keys 8w..8w+7 of the tile (mma.sync m16n8k16, fp32 accumulators)
+//   softmax      row maxima / sums exchanged through shared memory, fp32, every warp keeps the same running (m, l)
+//   O [16 x lat] += P [16 x 32] . C          warp w owns latent columns [w lat/4, (w+1) lat/4); the B fragments come out of
+//                                            the row-major key tile with ldmatrix.trans, so the tile is staged once and
+//                                            serves as K and as V
+// Key tiles arrive through a two-stage cp.async ring (16-byte copies, zero-filled past the row's position, so nothing
+// uninitialised in the pool can reach an accumulator).  With nsplit > 1 (few rows, long contexts: decoding) the key tiles
+// are dealt to nsplit CTAs per (row, head group) whose unnormalised partial results are merged by a second kernel.
+constexpr int kTcHeads = 16;
+constexpr int kPsLd = kKeyTile + 8;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int NTO>   // n8 tiles of the latent per warp: lat = 32 * NTO
+__global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16* out, float* partial, const __nv_bfloat16* qa,
+                                                                   const __nv_bfloat16* pool, const int* tok_seq,
+                                                                   const int* tok_pos, const int* block_table, int max_blocks,
+                                                                   int page, int heads, int rot_dim, float scale, int nsplit) {
+  constexpr int LAT = NTO * 32;
+  const int D = LAT + rot_dim, LDK = D + 8, CH = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [16][LDK]
+  __nv_bfloat16* Ks = Qs + kTcHeads * LDK;                             // [2][32][LDK]
+  __nv_bfloat16* Ps = Ks + 2 * kKeyTile * LDK;                         // [16][40]
+  float* red = reinterpret_cast<float*>(Ps + kTcHeads * kPsLd);        // [2][4][16]: row maxima, row sums per warp
+  const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32, g = lane / 4, t = lane % 4;
+  const int row = blockIdx.x, hg = blockIdx.y, split = blockIdx.z;
+  const int pos = tok_pos[row];
+  const int* bt = block_table + (int64_t) tok_seq[row] * max_blocks;
+  const int tiles_total = pos / kKeyTile + 1;
+  const int per = (tiles_total + nsplit - 1) / nsplit;
+  const int t0 = split * per, t1 = min(tiles_total, t0 + per);
+
+  for (int e = tid; e < kTcHeads * CH; e += 128) {
+    const int r = e / CH, c = e % CH, head = hg * kTcHeads + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (head < heads) v = *reinterpret_cast<const uint4*>(qa + ((int64_t) row * heads + head) * D + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LDK + c * 8) = v;
+  }
+  auto load_tile = [&](int tile, int buf) {
+    const int j0 = tile * kKeyTile;
+    for (int e = tid; e < kKeyTile * CH; e += 128) {
+      const int jj = e / CH, c = e % CH, j = j0 + jj;
+      const bool ok = j <= pos;
+      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / page] * page + j % page) * D + c * 8 : pool;
+      cp_async16(Ks + (buf * kKeyTile + jj) * LDK + c * 8, src, ok ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[NTO][4];
+#pragma unroll
+  for (int n = 0; n < NTO; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  if (t0 < t1) load_tile(t0, 0);
+  for (int tile = t0; tile < t1; ++tile) {
+    const int buf = (tile - t0) & 1;
+    if (tile + 1 < t1) {
+      load_tile(tile + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* Kb = Ks + buf * kKeyTile * LDK;
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+      const __nv_bfloat16* qr = Qs + g * LDK + 2 * t;
+      const __nv_bfloat16* kr = Kb + (warp * 8 + g) * LDK + 2 * t;
+#pragma unroll 4
+      for (int kk = 0; kk < D; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(qr + kk);
+        a[1] = *reinterpret_cast<const uint32_t*>(qr + 8 * LDK + kk);
+        a[2] = *reinterpret_cast<const uint32_t*>(qr + kk + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qr + 8 * LDK + kk + 8);
+        mma_bf16_16816(s, a, *reinterpret_cast<const uint32_t*>(kr + kk), *reinterpret_cast<const uint32_t*>(kr + kk + 8));
+      }
+    }
+    const int j = tile * kKeyTile + warp * 8 + 2 * t;
+    s[0] = j <= pos ? s[0] * scale : -INFINITY;
+    s[1] = j + 1 <= pos ? s[1] * scale : -INFINITY;
+    s[2] = j <= pos ? s[2] * scale : -INFINITY;
+    s[3] = j + 1 <= pos ? s[3] * scale : -INFINITY;
+    float mx0 = fmaxf(s[0], s[1]), mx1 = fmaxf(s[2], s[3]);
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (t == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
+    __syncthreads();
+    float mn0 = m0, mn1 = m1;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { mn0 = fmaxf(mn0, red[w * 16 + g]); mn1 = fmaxf(mn1, red[w * 16 + g + 8]); }
+    // mn finite: the tile's first key is visible to every row
+    const __nv_bfloat162 p01 = __floats2bfloat162_rn(__expf(s[0] - mn0), __expf(s[1] - mn0));
+    const __nv_bfloat162 p23 = __floats2bfloat162_rn(__expf(s[2] - mn1), __expf(s[3] - mn1));
+    *reinterpret_cast<__nv_bfloat162*>(Ps + g * kPsLd + warp * 8 + 2 * t) = p01;
+    *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * kPsLd + warp * 8 + 2 * t) = p23;
+    float ps0 = __bfloat162float(p01.x) + __bfloat162float(p01.y), ps1 = __bfloat162float(p23.x) + __bfloat162float(p23.y);
+    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1);
+    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
+    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1);
+    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
+    if (t == 0) { red[64 + warp * 16 + g] = ps0; red[64 + warp * 16 + g + 8] = ps1; }
+    __syncthreads();
+    const float c0 = __expf(m0 - mn0), c1 = __expf(m1 - mn1);     // 0 on the first tile
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) { sum0 += red[64 + w * 16 + g]; sum1 += red[64 + w * 16 + g + 8]; }
+    l0 = l0 * c0 + sum0;
+    l1 = l1 * c1 + sum1;
+    m0 = mn0;
+    m1 = mn1;
+#pragma unroll
+    for (int n = 0; n < NTO; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+    for (int kk = 0; kk < kKeyTile; kk += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(Ps + g * kPsLd + kk + 2 * t);
+      a[1] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * kPsLd + kk + 2 * t);
+      a[2] = *reinterpret_cast<const uint32_t*>(Ps + g * kPsLd + kk + 2 * t + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * kPsLd + kk + 2 * t + 8);
+      const uint32_t kaddr = (uint32_t) __cvta_generic_to_shared(Kb + (kk + (lane & 15)) * LDK + warp * (LAT / 4));
+#pragma unroll
+      for (int n = 0; n < NTO; ++n) {
+        uint32_t b0, b1;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(kaddr + n * 16));
+        mma_bf16_16816(o[n], a, b0, b1);
+      }
+    }
+    __syncthreads();
+  }
+
+  const int h0 = hg * kTcHeads + g, h1 = h0 + 8;
+  if (nsplit == 1) {
+    const float i0 = 1.f / l0, i1 = 1.f / l1;
+#pragma unroll
+    for (int n = 0; n < NTO; ++n) {
+      const int col = warp * (LAT / 4) + n * 8 + 2 * t;
+      if (h0 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t) row * heads + h0) * LAT + col) = __floats2bfloat162_rn(o[n][0] * i0, o[n][1] * i0);
+      if (h1 < heads)
+        *reinterpret_cast<__nv_bfloat162*>(out + ((int64_t) row * heads + h1) * LAT + col) = __floats2bfloat162_rn(o[n][2] * i1, o[n][3] * i1);
+    }
+  } else {
+    // partial [row][head][split][LAT + 2]: unnormalised sums, then the running maximum and the running sum
+#pragma unroll
+    for (int n = 0; n < NTO; ++n) {
+      const int col = warp * (LAT / 4) + n * 8 + 2 * t;
+      if (h0 < heads) {
+        float* d = partial + (((int64_t) row * heads + h0) * nsplit + split) * (LAT + 2);
+        d[col] = o[n][0]; d[col + 1] = o[n][1];
+      }
+      if (h1 < heads) {
+        float* d = partial + (((int64_t) row * heads + h1) * nsplit + split) * (LAT + 2);
+        d[col] = o[n][2]; d[col + 1] = o[n][3];
+      }
+    }
+    if (warp == 0 && t == 0) {
+      if (h0 < heads) { float* d = partial + (((int64_t) row * heads + h0) * nsplit + split) * (LAT + 2); d[LAT] = m0; d[LAT + 1] = l0; }
+      if (h1 < heads) { float* d = partial + (((int64_t) row * heads + h1) * nsplit + split) * (LAT + 2); d[LAT] = m1; d[LAT + 1] = l1; }
+    }
+  }
+}
+
+// one CTA per (row, head): out = sum_s o_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in index order
+__global__ void latent_attention_merge_kernel(__nv_bfloat16* out, const float* partial, int lat, int nsplit) {
+  const int64_t rh = blockIdx.x;
+  const float* p = partial + rh * nsplit * (lat + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p[s * (lat + 2) + lat]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float l = p[s * (lat + 2) + lat + 1];
+    if (l > 0.f) L += l * __expf(p[s * (lat + 2) + lat] - M);
+  }
+  const float inv = 1.f / L;
+  for (int c = threadIdx.x; c < lat; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float l = p[s * (lat + 2) + lat + 1];
+      if (l > 0.f) acc += p[s * (lat + 2) + c] * __expf(p[s * (lat + 2) + lat] - M);
+    }
+    out[rh * lat + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int NTO>
+int launch_latent_mma(__nv_bfloat16* out, float* partial, const __nv_bfloat16* qa, const __nv_bfloat16* pool, const int* tok_seq,
+                      const int* tok_pos, const int* block_table, int max_blocks, int page, int rows, int heads, int rot_dim,
+                      float scale, int nsplit, cudaStream_t s) {
+  const int D = NTO * 32 + rot_dim;
+  const size_t smem = (size_t) (kTcHeads + 2 * kKeyTile) * (D + 8) * 2 + kTcHeads * kPsLd * 2 + 2 * 4 * 16 * sizeof(float);
+  if (smem > 227 * 1024) return -2;
+  TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<NTO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  dim3 grid(rows, (heads + kTcHeads - 1) / kTcHeads, nsplit);
+  latent_attention_mma_kernel<NTO><<<grid, 128, smem, s>>>(out, partial, qa, pool, tok_seq, tok_pos, block_table, max_blocks,
+                                                           page, heads, rot_dim, scale, nsplit);
+  TB_CHECK_CUDA(cudaGetLastError());
+  if (nsplit > 1) {
+    latent_attention_merge_kernel<<<rows * heads, 128, 0, s>>>(out, partial, NTO * 32, nsplit);
+    TB_CHECK_CUDA(cudaGetLastError());
+  }
+  return 0;
 }
 
 }  // namespace
@@ -150,14 +372,36 @@ extern "C" int tb_latent_kv_append(void* pool, int dtype, const float* kv, int64
   return 0;
 }
 
+extern "C" int tb_latent_attention_tensor_cores(int dtype, int lat, int rot_dim) {
+  const int nto = lat / 32;
+  const bool have = nto == 1 || nto == 2 || nto == 3 || nto == 4 || nto == 5 || nto == 6 || nto == 8 || nto == 12 || nto == 16;
+  return dtype == TB_DT_BF16 && lat % 32 == 0 && have && rot_dim % 16 == 0;
+}
+
 extern "C" int tb_latent_attention(void* out, const void* qa, const void* pool, int dtype, const int* tok_seq,
                                    const int* tok_pos, const int* block_table, int max_blocks, int page, int rows, int heads,
-                                   int lat, int rot_dim, float scale, tb_stream_t stream) {
+                                   int lat, int rot_dim, float scale, int nsplit, float* workspace, tb_stream_t stream) {
   if (!out || !qa || !pool || !tok_seq || !tok_pos || !block_table || heads <= 0 || lat <= 0 || rot_dim < 0 || page <= 0 ||
       max_blocks <= 0 || rows < 0)
     return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (rows == 0) return 0;
+  if (tb_latent_attention_tensor_cores(dtype, lat, rot_dim) && (uintptr_t) qa % 16 == 0 && (uintptr_t) pool % 16 == 0 &&
+      (uintptr_t) out % 4 == 0) {
+    if (nsplit < 1 || !workspace) nsplit = 1;
+    if (nsplit > 64) nsplit = 64;
+#define TB_LAT_CASE(n)                                                                                                   \
+  case n:                                                                                                               \
+    return launch_latent_mma<n>((__nv_bfloat16*) out, workspace, (const __nv_bfloat16*) qa, (const __nv_bfloat16*) pool, \
+                                tok_seq, tok_pos, block_table, max_blocks, page, rows, heads, rot_dim, scale, nsplit,   \
+                                (cudaStream_t) stream);
+    switch (lat / 32) {
+      TB_LAT_CASE(1) TB_LAT_CASE(2) TB_LAT_CASE(3) TB_LAT_CASE(4) TB_LAT_CASE(5) TB_LAT_CASE(6) TB_LAT_CASE(8) TB_LAT_CASE(12)
+      TB_LAT_CASE(16)
+      default: break;
+    }
+#undef TB_LAT_CASE
+  }
   const int D = lat + rot_dim;
   const size_t smem = sizeof(float) * ((size_t) kKeyTile * (D + 1) + (size_t) kAttnWarps * (D + lat));
   if (smem > 227 * 1024) return -2;

@@ -6,9 +6,16 @@
 //   linear_fma_kernel   fp32 multiply-add with every product taken in fp32 (no TF32, no split-K): the all-32-bit mode and
 //                       the small block-diagonal products that feed a recurrence.  64 x 64 x 16 tiles, 4 x 4 per thread.
 //
-// Both walk k in one fixed order per output element, so a token's result is the same wherever it stands in a batch.
+//   linear_gemv_kernel  bf16 weights, at most 8 rows (generation steps): the step is bound by reading W once, so one warp
+//                       owns an output column, streams its weight row with 16-byte loads (4 in flight per lane) against
+//                       the rows staged once per CTA in shared memory as bf16, and reduces with shuffles.  Rows are
+//                       dealt to the warps of the whole grid round-robin, so the chip reads one contiguous window of W.
+//
+// All walk k in one fixed order per output element, so a token's result is the same wherever it stands in a batch.
 // blockIdx.z walks a batch of independent problems (per-head absorbed projections, block-diagonal gates).
 #include <cuda_bf16.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 #include "../../include/trtllm_b200_ragged.h"
@@ -201,6 +208,83 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
       }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+template <typename AT, typename CT, int MR>
+__global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p) {
+  extern __shared__ __align__(16) __nv_bfloat16 a_s[];          // [MR][K]
+  const int b = blockIdx.y;
+  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) b * p.w_bs;
+  CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
+  const int K = p.K;
+  for (int e = threadIdx.x; e < MR * K; e += 256) {
+    const int m = e / K, k = e - m * K;
+    a_s[e] = m < p.M ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) m * p.lda + k])) : __float2bfloat16_rn(0.f);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const __nv_bfloat16* bias = p.bias ? reinterpret_cast<const __nv_bfloat16*>(p.bias) + (int64_t) b * p.bias_bs : nullptr;
+  for (int n = blockIdx.x * 8 + warp; n < p.N; n += gridDim.x * 8) {
+    const __nv_bfloat16* wr = W + (int64_t) n * K;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+#pragma unroll 4
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr + k));
+      const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(w2[j]); wf[2 * j] = f.x; wf[2 * j + 1] = f.y; }
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        const uint4 av = *reinterpret_cast<const uint4*>(a_s + m * K + k);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(a2[j]);
+          acc[m] = fmaf(wf[2 * j], f.x, acc[m]);
+          acc[m] = fmaf(wf[2 * j + 1], f.y, acc[m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = warp_sum(acc[m]);
+    if (lane == 0) {
+      const float bv = bias ? __bfloat162float(bias[n]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < MR; ++m) {
+        if (m >= p.M) break;
+        float v = acc[m] + bv;
+        if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+        C[(int64_t) m * p.ldc + n] = from_f<CT>(v);
+      }
+    }
+  }
+}
+
+template <typename AT, typename CT>
+int launch_gemv(const LinArgs& p, int batch, cudaStream_t s) {
+  const int mr = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : 8));
+  const size_t smem = (size_t) mr * p.K * sizeof(__nv_bfloat16);
+  // enough CTAs to cover the chip a few times over, but no more warps than output columns
+  int ctas = (p.N + 7) / 8;
+  const int cap = std::max(1, 148 * 4 / batch);
+  if (ctas > cap) ctas = cap;
+  dim3 grid(ctas, batch);
+#define TB_GEMV_CASE(MR)                                                                                             \
+  case MR:                                                                                                           \
+    if (smem > 48 * 1024)                                                                                            \
+      TB_CHECK_CUDA(cudaFuncSetAttribute(linear_gemv_kernel<AT, CT, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         (int) smem));                                                               \
+    linear_gemv_kernel<AT, CT, MR><<<grid, 256, smem, s>>>(p);                                                       \
+    break;
+  switch (mr) { TB_GEMV_CASE(1) TB_GEMV_CASE(2) TB_GEMV_CASE(4) TB_GEMV_CASE(8) }
+#undef TB_GEMV_CASE
+  return 0;
+}
+
 template <typename AT, typename WT>
 int launch_fma(const LinArgs& p, int c_dtype, dim3 grid, cudaStream_t s) {
   if (c_dtype == TB_DT_F32) linear_fma_kernel<AT, WT, float><<<grid, 256, 0, s>>>(p);
@@ -222,7 +306,14 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
   LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
-  if (w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO) {
+  const bool gemv_ok = w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO && M <= 8 && K % 8 == 0 && (uintptr_t) w % 16 == 0 &&
+                       w_bs % 8 == 0 && (size_t) 8 * K * 2 <= 160 * 1024 && batch <= 65535;
+  if (gemv_ok) {
+    int rc;
+    if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, batch, s) : launch_gemv<float, __nv_bfloat16>(p, batch, s);
+    else rc = c_dtype == TB_DT_F32 ? launch_gemv<__nv_bfloat16, float>(p, batch, s) : launch_gemv<__nv_bfloat16, __nv_bfloat16>(p, batch, s);
+    if (rc) return rc;
+  } else if (w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO) {
     const int asz = a_dtype == TB_DT_F32 ? 4 : 2;
     const int vec_a = ((uintptr_t) a % 16 == 0) && (lda * asz % 16 == 0) && (a_bs * asz % 16 == 0);
     const int vec_w = ((uintptr_t) w % 16 == 0) && (K % 8 == 0) && (w_bs % 8 == 0);

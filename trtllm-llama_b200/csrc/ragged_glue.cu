@@ -68,6 +68,12 @@ __global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int6
   }
 }
 
+// fp32 rows (row stride ld) -> contiguous bf16: the residual stream as the operand of a tcgen05 projection
+__global__ void cast_rows_bf16_kernel(__nv_bfloat16* out, const float* x, int64_t ld, int cols, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16_rn(x[(i / cols) * ld + i % cols]);
+}
+
 __global__ void rope_table_kernel(float* table, const int* tok_pos, int rows, int half, int dims, double base) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * half) return;
@@ -135,6 +141,16 @@ extern "C" int tb_gated_act(void* out, int out_dtype, const float* gu, int rows,
   const int64_t n = (int64_t) rows * ff;
   const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
   gated_act_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, gu, n, ff, alpha, limit, up_shift);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_cast_rows_bf16(void* out, const float* x, int64_t ld, int rows, int cols, tb_stream_t stream) {
+  if (!out || !x || cols <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * cols;
+  const int grid = (int) ((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  cast_rows_bf16_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) out, x, ld, cols, n);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

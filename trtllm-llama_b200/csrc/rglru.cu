@@ -90,6 +90,73 @@ __global__ void rglru_scan_kernel(T* out, const float* u, const float* gates, co
   *sp = S;
 }
 
+
+// Chunked form for long portions (prefill): the recurrence S_t = a_t S_(t-1) + b_t composes, so a sequence's rows are cut
+// into chunks of kScanChunk; (1) every (chunk, channel) scans its rows from zero and keeps the product of its a's and its
+// final value, (2) one thread per (sequence, channel) walks the chunk summaries in order, leaves every chunk's incoming
+// state and the sequence's new state, (3) every (chunk, channel) scans again from its incoming state and writes S * y.
+// Gates are recomputed in (3) instead of stored: two transcendental passes cost less than 16 bytes per element of traffic.
+constexpr int kScanChunk = 64;
+
+struct GateCoef { float a, b; };
+__device__ __forceinline__ GateCoef rglru_coef(float gr, float gi, float uv, float c_sp) {
+  const float r = 1.f / (1.f + expf(-gr));
+  const float ig = 1.f / (1.f + expf(-gi));
+  const float la = -c_sp * r;
+  GateCoef k;
+  k.a = expf(la);
+  k.b = sqrtf(-expm1f(2.f * la)) * ig * uv;
+  return k;
+}
+
+// grid (ceil(C / 128), max_chunks, seqs)
+template <typename T, int PHASE>
+__global__ void __launch_bounds__(128) rglru_chunk_kernel(T* out, const float* u, const float* gates, const void* lam, int w_dtype,
+                                                          const T* y, float* ws, const int* seq_start, const int* seq_len,
+                                                          int channels, int blocks, float c, int max_chunks) {
+  const int ch = blockIdx.x * 128 + threadIdx.x, chunk = blockIdx.y, e = blockIdx.z;
+  if (ch >= channels) return;
+  const int len = seq_len[e], r0 = chunk * kScanChunk;
+  if (r0 >= len) return;
+  const int r1 = min(len, r0 + kScanChunk);
+  const int bw = channels / blocks, b = ch / bw, j = ch % bw;
+  const float lm = ld_w(lam, w_dtype, ch);
+  const float c_sp = c * (lm > 20.f ? lm : log1pf(expf(lm)));
+  const int64_t g_r = (int64_t) (b * 2) * bw + j, g_i = g_r + bw;
+  const int64_t slot = ((int64_t) e * max_chunks + chunk) * channels + ch, plane = (int64_t) gridDim.z * max_chunks * channels;
+  float S = PHASE == 1 ? 0.f : ws[2 * plane + slot], P = 1.f;
+  for (int64_t row = seq_start[e] + r0; row < seq_start[e] + r1; ++row) {
+    const GateCoef k = rglru_coef(gates[row * 2 * channels + g_r], gates[row * 2 * channels + g_i], u[row * channels + ch], c_sp);
+    S = fmaf(k.a, S, k.b);
+    if (PHASE == 1) {
+      P *= k.a;
+    } else {
+      float yv;
+      if constexpr (sizeof(T) == 4) yv = y[row * channels + ch]; else yv = __bfloat162float(y[row * channels + ch]);
+      if constexpr (sizeof(T) == 4) out[row * channels + ch] = S * yv; else out[row * channels + ch] = __float2bfloat16_rn(S * yv);
+    }
+  }
+  if (PHASE == 1) { ws[slot] = P; ws[plane + slot] = S; }
+}
+
+// one thread per (sequence, channel): carry the state through the chunk summaries
+__global__ void rglru_carry_kernel(float* ws, float* state, const int* seq_len, const int* seq_past, const int* seq_slot, int seqs,
+                                   int channels, int max_chunks) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= seqs * channels) return;
+  const int e = i / channels, ch = i % channels;
+  const int chunks = (seq_len[e] + kScanChunk - 1) / kScanChunk;
+  const int64_t plane = (int64_t) seqs * max_chunks * channels;
+  float* sp = state + (int64_t) seq_slot[e] * channels + ch;
+  float S = seq_past[e] > 0 ? *sp : 0.f;
+  for (int k = 0; k < chunks; ++k) {
+    const int64_t slot = ((int64_t) e * max_chunks + k) * channels + ch;
+    ws[2 * plane + slot] = S;
+    S = fmaf(ws[slot], S, ws[plane + slot]);
+  }
+  *sp = S;
+}
+
 }  // namespace
 }  // namespace tb
 
@@ -125,7 +192,8 @@ extern "C" int tb_causal_conv1d_update(float* state, const float* x, const int* 
 
 extern "C" int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, const void* lam, int w_dtype,
                              const void* y, float* state, const int* seq_start, const int* seq_len, const int* seq_past,
-                             const int* seq_slot, int seqs, int channels, int blocks, float c, tb_stream_t stream) {
+                             const int* seq_slot, int seqs, int channels, int blocks, float c, int max_len, float* workspace,
+                             tb_stream_t stream) {
   if (!out || !u || !gates || !lam || !y || !state || !seq_start || !seq_len || !seq_past || !seq_slot || channels <= 0 ||
       blocks <= 0 || channels % blocks || seqs < 0)
     return -1;
@@ -133,6 +201,28 @@ extern "C" int tb_rglru_scan(void* out, int dtype, const float* u, const float* 
   if (seqs == 0) return 0;
   const int n = seqs * channels;
   cudaStream_t s = (cudaStream_t) stream;
+  if (workspace && max_len > kScanChunk && seqs <= 65535) {
+    const int max_chunks = (max_len + kScanChunk - 1) / kScanChunk;
+    if (max_chunks > 65535) return -2;
+    dim3 grid((channels + 127) / 128, max_chunks, seqs);
+    if (dtype == TB_DT_F32) {
+      rglru_chunk_kernel<float, 1><<<grid, 128, 0, s>>>((float*) out, u, gates, lam, w_dtype, (const float*) y, workspace,
+                                                        seq_start, seq_len, channels, blocks, c, max_chunks);
+      rglru_carry_kernel<<<(n + 127) / 128, 128, 0, s>>>(workspace, state, seq_len, seq_past, seq_slot, seqs, channels, max_chunks);
+      rglru_chunk_kernel<float, 2><<<grid, 128, 0, s>>>((float*) out, u, gates, lam, w_dtype, (const float*) y, workspace,
+                                                        seq_start, seq_len, channels, blocks, c, max_chunks);
+    } else {
+      rglru_chunk_kernel<__nv_bfloat16, 1><<<grid, 128, 0, s>>>((__nv_bfloat16*) out, u, gates, lam, w_dtype,
+                                                                (const __nv_bfloat16*) y, workspace, seq_start, seq_len,
+                                                                channels, blocks, c, max_chunks);
+      rglru_carry_kernel<<<(n + 127) / 128, 128, 0, s>>>(workspace, state, seq_len, seq_past, seq_slot, seqs, channels, max_chunks);
+      rglru_chunk_kernel<__nv_bfloat16, 2><<<grid, 128, 0, s>>>((__nv_bfloat16*) out, u, gates, lam, w_dtype,
+                                                                (const __nv_bfloat16*) y, workspace, seq_start, seq_len,
+                                                                channels, blocks, c, max_chunks);
+    }
+    TB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (dtype == TB_DT_F32)
     rglru_scan_kernel<float><<<(n + 63) / 64, 64, 0, s>>>((float*) out, u, gates, lam, w_dtype, (const float*) y, state,
                                                           seq_start, seq_len, seq_past, seq_slot, seqs, channels, blocks, c);

@@ -60,6 +60,8 @@ class RaggedBatch:
             tok_pos += range(p, p + len(toks))
             table += list(blocks) + [-1] * (self.max_blocks - len(blocks))
         self.num_rows, self.num_seqs, self.num_want = len(tok_ids), len(entries), len(want_rows)
+        self.max_len = max(length)        # ... and by the longest portion
+        self.max_pos = max(tok_pos)       # host-side hint for kernels that size their grids by context length
         parts = [tok_ids, tok_seq, tok_pos, start, length, past, slot, table, list(want_rows)]
         host = torch.tensor([v for p in parts for v in p], dtype=torch.int32)
         if torch.device(device).type == "cuda":

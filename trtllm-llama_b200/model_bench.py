@@ -1,0 +1,261 @@
+"""``bench.py --model zobasun``: prefill and decode throughput of the in-flight served design at layer sizes that resemble
+real models (random bf16 weights), beside a LLaMA engine of equal width / depth / feed-forward size served by
+``GenerationSession`` (fp16), and every operator's distance from its roofline.
+
+Timing: CUDA events on the launching stream, >= 3 warm-up runs; every timed run works on tensors far larger than L2 or is
+preceded by an L2 flush (a 256 MB fill).  Roofline denominators: MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 burst)."""
+from __future__ import annotations
+
+import json
+import os
+
+SIZES = {
+    # name: width, heads, dim, rot_dim, vdim, kv_rank, q_rank, ff, recurrent width, blocks, vocab
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768, ff=5632, rnn=2048, blocks=16, vocab=32000),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536, ff=11008, rnn=4096, blocks=32, vocab=32000),
+}
+
+
+def random_zobasun(torch, s, seed=0):
+    """config + bf16 tensors of a 4-layer stack: latent attention, latent attention on the first layer's cache, two
+    gated linear recurrences; every layer with a feed-forward."""
+    g = torch.Generator().manual_seed(seed)
+    W = s["width"]
+
+    def n(*shape, std=None):
+        std = std if std is not None else shape[-1] ** -0.5
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    att = dict(heads=s["heads"], dim=s["dim"], rot_dim=s["rot_dim"], vdim=s["vdim"], kv_rank=s["kv_rank"], q_rank=s["q_rank"],
+               scale=(s["dim"] + s["rot_dim"]) ** -0.5, rot=dict(base=10000.0, dims=s["rot_dim"]))
+    rec = dict(width=s["rnn"], blocks=s["blocks"], conv=4)
+    mlp = dict(kind="dense", ff=s["ff"], limit=7.0)
+    layers = [dict(type="latent_attention", mixer=dict(att), mlp=mlp),
+              dict(type="latent_attention", mixer=dict(att, kv_from=0), mlp=mlp),
+              dict(type="rglru", mixer=rec, mlp=mlp), dict(type="rglru", mixer=rec, mlp=mlp)]
+    cfg = dict(architecture="Zobasun", vocab=s["vocab"], width=W, embedding=dict(scale=1.0), norm=dict(eps=1e-6), layers=layers)
+    t = {"embed": n(s["vocab"], W, std=1.0), "head": n(s["vocab"], W), "final.norm": n(W, std=0.1)}
+    H, dn, dr, dv, R, Q, C, nb = s["heads"], s["dim"], s["rot_dim"], s["vdim"], s["kv_rank"], s["q_rank"], s["rnn"], s["blocks"]
+    for i, l in enumerate(layers):
+        p = f"l{i}."
+        t[p + "norm1"], t[p + "norm2"] = n(W, std=0.1), n(W, std=0.1)
+        if l["type"] == "latent_attention":
+            t.update({p + "mix.dq": n(Q, W), p + "mix.dq.norm": n(Q, std=0.1) + 1, p + "mix.uq": n(H * (dn + dr), Q),
+                      p + "mix.uk": n(H * dn, R), p + "mix.uv": n(H * dv, R), p + "mix.o": n(W, H * dv)})
+            if "kv_from" not in l["mixer"]:
+                t.update({p + "mix.dkv": n(R + dr, W), p + "mix.dkv.norm": n(R, std=0.1) + 1})
+        else:
+            bw = C // nb
+            t.update({p + "mix.y": n(C, W), p + "mix.y.b": n(C, std=0.1), p + "mix.x": n(C, W), p + "mix.x.b": n(C, std=0.1),
+                      p + "mix.conv": n(C, 4, std=0.5), p + "mix.conv.b": n(C, std=0.1), p + "mix.ra": n(nb, bw, bw),
+                      p + "mix.ra.b": n(nb, bw, std=0.1), p + "mix.ri": n(nb, bw, bw), p + "mix.ri.b": n(nb, bw, std=0.1),
+                      p + "mix.lam": n(C, std=1.0), p + "mix.o": n(W, C)})
+        t.update({p + "mlp.gate": n(s["ff"], W), p + "mlp.up": n(s["ff"], W), p + "mlp.down": n(W, s["ff"])})
+    return cfg, t
+
+
+class OpTimer:
+    """Wraps the ragged operators of ``ops`` with CUDA-event timers and the bytes / flops each call moves."""
+
+    NAMES = ("linear", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
+             "latent_attention", "causal_conv1d", "rglru_scan")
+
+    def __init__(self, torch, ops):
+        self.torch, self.ops, self.rec, self.saved = torch, ops, [], {}
+
+    @staticmethod
+    def _nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts if t is not None)
+
+    def _cost(self, name, args, kw, out):
+        nb = self._nbytes
+        if name == "linear":
+            a, w = args[0], args[1]
+            o = kw.get("out", out)
+            B = w.shape[0] if w.dim() == 3 else 1
+            N, K = w.shape[-2], w.shape[-1]
+            return "linear", 2.0 * a.shape[0] * N * K * B, nb(w) + a.shape[0] * B * K * a.element_size() + nb(o)
+        if name == "latent_attention":
+            qa, pool, batch = args[0], args[1], args[2]
+            heads, lat, rot = args[4], args[5], args[6]
+            pos = batch._host[batch.num_rows * 2:batch.num_rows * 3].double()
+            keys = float((pos + 1).sum())
+            # minimal traffic: every sequence's cache entries once, queries and outputs once
+            seqlen = {}
+            for s, p in zip(batch._host[batch.num_rows:batch.num_rows * 2].tolist(), pos.tolist()):
+                seqlen[s] = max(seqlen.get(s, 0), p + 1)
+            return name, 2.0 * keys * heads * (2 * lat + rot), sum(seqlen.values()) * (lat + rot) * pool.element_size() + nb(qa, out)
+        if name == "latent_kv_append":
+            pool, kv, lat, rot = args[0], args[1], args[8], args[9]
+            return name, 0.0, kv.shape[0] * (lat + rot) * (4 + pool.element_size())
+        if name == "causal_conv1d":
+            return name, 0.0, 2 * nb(args[0])
+        if name == "rglru_scan":
+            return name, 0.0, nb(args[0], args[1], args[3], out)
+        ts = [a for a in args if isinstance(a, self.torch.Tensor)] + [v for v in kw.values() if isinstance(v, self.torch.Tensor)]
+        if isinstance(out, self.torch.Tensor) and all(out is not x for x in ts):
+            ts.append(out)
+        return name, 0.0, nb(*ts)
+
+    def __enter__(self):
+        torch = self.torch
+        for nm in self.NAMES:
+            fn = getattr(self.ops, nm)
+            self.saved[nm] = fn
+
+            def wrapped(*a, _fn=fn, _nm=nm, **kw):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = _fn(*a, **kw)
+                e1.record()
+                self.rec.append((self._cost(_nm, a, kw, out), e0, e1))
+                return out
+            setattr(self.ops, nm, wrapped)
+        return self
+
+    def __exit__(self, *exc):
+        for nm, fn in self.saved.items():
+            setattr(self.ops, nm, fn)
+
+    def summary(self, peaks):
+        self.torch.cuda.synchronize()
+        agg = {}
+        for (name, flops, nbytes), e0, e1 in self.rec:
+            a = agg.setdefault(name, [0.0, 0.0, 0.0, 0])
+            a[0] += e0.elapsed_time(e1) * 1e-3
+            a[1] += flops
+            a[2] += nbytes
+            a[3] += 1
+        out = {}
+        for name, (t, fl, by, calls) in agg.items():
+            ideal = max(fl / (peaks["bf16_tflops"] * 1e12), by / (peaks["hbm_gbs"] * 1e9))
+            out[name] = {"calls": calls, "us": round(t * 1e6, 1), "tflops": round(fl / t / 1e12, 1), "gbs": round(by / t / 1e9, 1),
+                         "of_roofline": round(ideal / t, 3)}
+        return out
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _time(torch, fn, steps, warmup, flush):
+    for _ in range(max(3, warmup)):
+        fn()
+    ts = []
+    for _ in range(steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return sorted(ts)[len(ts) // 2]
+
+
+def bench_size(torch, name, steps, warmup, S=2048, B=4):
+    from . import ops
+    from . import runtime as rt
+    from .inflight import InflightSession
+    from .models.zobasun import build_zobasun
+    s, peaks = SIZES[name], _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cfg, tensors = random_zobasun(torch, s)
+    model = build_zobasun(cfg, tensors, torch.bfloat16, "cuda")
+    del tensors
+    sess = InflightSession(model, max_tokens=(B + 1) * (S + 64), max_seqs=B + 1)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, s["vocab"], (S,), generator=g).tolist()
+    res = {"size": dict(s), "layers": [l["type"] + ("+kv_from" if "kv_from" in l["mixer"] else "") for l in cfg["layers"]],
+           "prefill_tokens": S, "decode_batch": B, "decode_context": S}
+
+    def prefill():
+        sess.step([("p", prompt, [S - 1])])
+        sess.end("p")
+    t = _time(torch, prefill, steps, warmup, flush)
+    res["prefill_tokens_per_s"] = round(S / t, 1)
+    with OpTimer(torch, ops) as ot:
+        prefill()
+    res["prefill_ops"] = ot.summary(peaks)
+    for b in range(B):
+        sess.step([(("d", b), prompt, [])])
+    dec = [(("d", b), [7 + b], [0]) for b in range(B)]
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_tokens_per_s"] = round(B / t, 1)
+    res["decode_ms_per_step"] = round(t * 1e3, 3)
+    with OpTimer(torch, ops) as ot:
+        sess.step(dec)
+    res["decode_ops"] = ot.summary(peaks)
+    del sess, model
+    torch.cuda.empty_cache()
+
+    # the closest existing model at equal size: LLaMA (MHA, SwiGLU), fp16, same width / depth / feed-forward / vocabulary
+    import bench as HB
+    L = {"hidden": s["width"], "inter": s["ff"], "vocab": s["vocab"], "layers": len(cfg["layers"]), "heads": s["width"] // 128}
+    mc = rt.ModelConfig(vocab_size=L["vocab"], num_layers=L["layers"], num_heads=L["heads"], hidden_size=L["hidden"],
+                        inter_size=L["inter"], max_batch_size=B, max_input_len=S, max_output_len=64)
+    lt = rt.build_engine_tensors(HB.make_weights(torch, L, 0, 1), mc)
+    ls = rt.GenerationSession(mc, lt)
+    ls.setup(B, S, 64)
+    ids1 = torch.tensor([prompt], dtype=torch.int32)
+    t = _time(torch, lambda: ls.context(ids1, torch.tensor([S], dtype=torch.int32)), steps, warmup, flush)
+    res["llama_prefill_tokens_per_s"] = round(S / t, 1)
+    idsB = ids1.repeat(B, 1)
+    ls.context(idsB, torch.tensor([S] * B, dtype=torch.int32))
+    ts = []
+    for i in range(max(3, warmup) + steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ls.step()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= max(3, warmup):
+            ts.append(e0.elapsed_time(e1) * 1e-3)
+    t = sorted(ts)[len(ts) // 2]
+    res["llama_decode_tokens_per_s"] = round(B / t, 1)
+    res["llama_decode_ms_per_step"] = round(t * 1e3, 3)
+    # like kernels, timed alone on the same shapes: prefill / decode projection, prefill / decode attention
+    like = {}
+    x = torch.randn(S, L["hidden"], device="cuda").half()
+    w = lt["layers.0.mlp.fc_gate.weight"]
+    fl = 2.0 * S * w.shape[0] * w.shape[1]
+    t = _time(torch, lambda: ops.matmul_f16(x, w), steps, warmup, flush)
+    like["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    xd = x[:B].contiguous()
+    t = _time(torch, lambda: ops.matmul_f16(xd, w), steps, warmup, flush)
+    like["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(w.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    H = L["heads"]
+    qkv = torch.randn(1, S, 3 * H * 128, device="cuda").half()
+    kvc = torch.zeros(B, 2, H, S + 64, 128, device="cuda", dtype=torch.float16)
+    lens1 = torch.tensor([S], dtype=torch.int32, device="cuda")
+    t = _time(torch, lambda: ops.context_attention(qkv, kvc, lens1, num_heads=H, head_size=128), steps, warmup, flush)
+    like["attention_prefill"] = {"us": round(t * 1e6, 1),
+                                 "of_roofline": round(4.0 * S * S / 2 * 128 * H / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    qd = torch.randn(B, 3 * H * 128, device="cuda").half()
+    t = _time(torch, lambda: ops.mmha_decode(qd, kvc, S, num_heads=H, head_size=128, max_input_len=S), steps, warmup, flush)
+    like["attention_decode"] = {"us": round(t * 1e6, 1),
+                                "of_roofline": round(B * 2 * H * S * 128 * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    res["llama_like_kernels"] = like
+    res["peaks"] = peaks
+    del ls, lt
+    torch.cuda.empty_cache()
+    return res
+
+
+def run(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --model needs a B200 (sm_100a): there is no CPU path")
+    names = args.model_sizes.split(",") if args.model_sizes else list(SIZES)
+    out = {"bench": "model_compare", "model": args.model, "dtype": "bf16 (llama: fp16)", "data": "synthetic",
+           "steps": args.steps, "warmup": max(3, args.warmup), "sizes": {}}
+    for nm in names:
+        out["sizes"][nm] = bench_size(torch, nm, args.steps, args.warmup)
+    print(json.dumps(out))

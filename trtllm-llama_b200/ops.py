@@ -345,6 +345,8 @@ from ._lib import ragged_lib as _rl  # noqa: E402
 DT_F32, DT_BF16 = 1, 2
 ACT_NONE, ACT_GELU_TANH = 0, 1
 COMPUTE_AUTO, COMPUTE_FMA32 = 0, 1
+# rows from which a bf16 projection goes to the tcgen05 kernel; below, the streaming GEMV (<= 8 rows) or the warp-MMA tiles
+TC_MIN_ROWS = 17
 
 
 def _dt(t):
@@ -389,8 +391,27 @@ def linear(a, w, bias=None, out=None, out_dtype=None, act=ACT_NONE, compute=COMP
         lda, a_bs, ldc, c_bs, w_bs, b_bs = a.stride(0), 0, out.stride(0), 0, 0, 0
     if bias is not None and bias.dtype != w.dtype:
         raise TypeError("bias must have the weight's type")
+    if (not batched and M >= TC_MIN_ROWS and compute == COMPUTE_AUTO and w.dtype == torch.bfloat16 and K % 8 == 0
+            and out.stride(0) == N and out.dtype in (torch.float32, torch.bfloat16)):
+        # prompt-sized bf16 products: the tcgen05 kernel.  fp32 rows (the residual stream) are rounded to bf16 once.
+        if a.dtype != torch.bfloat16 or a.stride(0) != K:
+            a = cast_rows_bf16(a)
+        ws = _workspace(1 << 22, a.device)
+        check(_rl.tb_gemm_tc_bf16(_p(out), 1 if out.dtype == torch.float32 else 3, _p(a), _p(w), _p(bias), act, M, N, K,
+                                  _p(ws), ws.numel(), _p(_counters(a.device)), _stream()), "tb_gemm_tc_bf16")
+        return out
     check(_rl.tb_linear(_p(out), _dt(out), ldc, c_bs, _p(a), _dt(a), lda, a_bs, _p(w), _dt(w), w_bs, _p(bias), b_bs,
                         M, N, K, B, act, compute, _stream()), "tb_linear")
+    return out
+
+
+def cast_rows_bf16(x):
+    """fp32 [rows, cols] (any row stride) -> contiguous bf16."""
+    _chk_dev(x)
+    if x.dtype == torch.bfloat16:
+        return x.contiguous()
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    check(_rl.tb_cast_rows_bf16(_p(out), _p(x), x.stride(0), x.shape[0], x.shape[1], _stream()), "tb_cast_rows_bf16")
     return out
 
 
@@ -447,11 +468,20 @@ def latent_kv_append(pool, kv, w, eps, table, dims, batch, page, lat, rot_dim):
 
 
 def latent_attention(qa, pool, batch, page, heads, lat, rot_dim, scale):
+    """Causal multi-query attention of every row over its sequence's cache entries.  Steps with few rows and long
+    contexts (decoding) deal each row's keys to several CTAs so that the whole chip reads the cache."""
     _chk_cuda(qa, pool)
-    out = torch.empty((qa.shape[0], heads, lat), dtype=qa.dtype, device=qa.device)
+    rows = qa.shape[0]
+    out = torch.empty((rows, heads, lat), dtype=qa.dtype, device=qa.device)
+    nsplit, ws = 1, None
+    if _rl.tb_latent_attention_tensor_cores(_dt(pool), lat, rot_dim):
+        ctas = rows * -(-heads // 16)
+        nsplit = max(1, min(32, 296 // ctas, (batch.max_pos + 1) // 128))
+        if nsplit > 1:
+            ws = torch.empty((rows * heads * nsplit * (lat + 2),), dtype=torch.float32, device=qa.device)
     check(_rl.tb_latent_attention(_p(out), _p(qa), _p(pool), _dt(pool), _p(batch.tok_seq), _p(batch.tok_pos),
-                                  _p(batch.block_table), batch.max_blocks, page, qa.shape[0], heads, lat, rot_dim,
-                                  float(scale), _stream()), "tb_latent_attention")
+                                  _p(batch.block_table), batch.max_blocks, page, rows, heads, lat, rot_dim,
+                                  float(scale), nsplit, _p(ws), _stream()), "tb_latent_attention")
     return out
 
 
@@ -472,9 +502,12 @@ def causal_conv1d(x, w, bias, state, batch):
 def rglru_scan(u, gates, lam, y, state, batch, blocks, c):
     _chk_cuda(u, gates, lam, y, state)
     out = torch.empty_like(y)
+    ws = None
+    if batch.max_len > 64:          # long portions: parallel chunks of 64 rows, summaries carried in order
+        ws = torch.empty((3 * batch.num_seqs * -(-batch.max_len // 64) * u.shape[1],), dtype=torch.float32, device=u.device)
     check(_rl.tb_rglru_scan(_p(out), _dt(out), _p(u), _p(gates), _p(lam), _dt(lam), _p(y), _p(state), _p(batch.seq_start),
                             _p(batch.seq_len), _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, u.shape[1], blocks,
-                            float(c), _stream()), "tb_rglru_scan")
+                            float(c), batch.max_len, _p(ws), _stream()), "tb_rglru_scan")
     return out
 
 
