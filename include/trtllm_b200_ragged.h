@@ -107,8 +107,8 @@ int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, 
  *   r = sigmoid(gr), i = sigmoid(gi), log a = -c * r * softplus(lam), S <- exp(log a) * S + sqrt(1 - exp(2 log a)) * i * u
  * with S read from / written to state[slot] (fp32 [slots, C]; zero at a sequence's first position), and
  * out[n, ch] = S * y[n, ch] stored as T.  u fp32 [N, C], y T [N, C], lam w_dtype [C].
- * max_len: the longest seq_len (host); with workspace (fp32, 3 * seqs * ceil(max_len / 64) * C) and max_len > 64 the rows
- * of a sequence are scanned in parallel chunks of 64 whose summaries are carried in order. */
+ * max_len: the longest seq_len (host); with workspace (fp32, 3 * seqs * ceil(max_len / 32) * C) and max_len > 32 the rows
+ * of a sequence are scanned in parallel chunks of 32 whose summaries are carried in order. */
 int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, const void* lam, int w_dtype, const void* y,
                   float* state, const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot,
                   int seqs, int channels, int blocks, float c, int max_len, float* workspace, tb_stream_t stream);

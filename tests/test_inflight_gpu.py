@@ -277,15 +277,20 @@ def test_mixed_batches_and_reuse(dtype, name):
         _close(torch.cat(got[k]), want[k], dtype, f"{name}: request {k} in mixed batches", scale=2.0)
 
 
+@pytest.mark.parametrize("graph", [True, False], ids=["replayed-graph", "eager"])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_long_decoding_across_pages(dtype):
+def test_long_decoding_across_pages(dtype, graph):
+    """Generation steps are replayed CUDA graphs (re-captured when the block table outgrows its width); the eager
+    launches of the same step must give the same answer."""
     cfg, t, model = _model("tc", dtype, seed=2)
     toks = _tokens(20 + 180, cfg["vocab"], 30)
     want = _oracle("tc", 2, toks)
     sess = _session(model, max_tokens=208, page=16)
+    sess.use_cuda_graph = graph
     rows = [sess.step([("a", toks[:20], [19])])[0]]
     rows += [sess.step([("a", [tok], [0])])[0] for tok in toks[20:]]
     _close(torch.stack(rows), want[19:], dtype, "180 decoded tokens", scale=2.0)
+    assert bool(sess._graphs) == graph
 
 
 def test_pool_exhaustion_is_refused_cleanly():

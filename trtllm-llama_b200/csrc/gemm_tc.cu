@@ -254,7 +254,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           tmem_ld16(t_addr + c * 16, v);
           tmem_ld_wait();
           const int mc = m0 + c * 16;
-          if (n < p.N && mc + 16 <= p.M && p.out_type == 0) {
+          if (KIND == kGF16 && p.bf16 && n < p.N && mc + 16 <= p.M) {
+            // bf16 operands, a full chunk: bias, activation and the store without per-element bounds checks
+            float f[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              f[j] = __uint_as_float(v[j]) + bias_n;
+              if (p.act == 1) f[j] = 0.5f * f[j] * (1.f + tanhf(0.7978845608028654f * (f[j] + 0.044715f * f[j] * f[j] * f[j])));
+            }
+            if (p.out_type == 3) {
+              __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.c) + (size_t) mc * p.N + n;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) cp[(size_t) j * p.N] = __float2bfloat16_rn(f[j]);
+            } else {
+              float* cp = reinterpret_cast<float*>(p.c) + (size_t) mc * p.N + n;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) cp[(size_t) j * p.N] = f[j];
+            }
+          } else if (n < p.N && mc + 16 <= p.M && p.out_type == 0) {
             // fast path: a full chunk of fp16 outputs, no per-element branches
             float f[16];
 #pragma unroll

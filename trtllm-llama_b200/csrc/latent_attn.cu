@@ -150,6 +150,18 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 template <int NTO>   // n8 tiles of the latent per warp: lat = 32 * NTO
 __global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16* out, float* partial, const __nv_bfloat16* qa,
                                                                    const __nv_bfloat16* pool, const int* tok_seq,
@@ -169,6 +181,7 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16
   const int tiles_total = pos / kKeyTile + 1;
   const int per = (tiles_total + nsplit - 1) / nsplit;
   const int t0 = split * per, t1 = min(tiles_total, t0 + per);
+  const int page_shift = 31 - __clz(page), page_mask = page - 1;        // pages are powers of two (checked by the launcher)
 
   for (int e = tid; e < kTcHeads * CH; e += 128) {
     const int r = e / CH, c = e % CH, head = hg * kTcHeads + r;
@@ -176,13 +189,16 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16
     if (head < heads) v = *reinterpret_cast<const uint4*>(qa + ((int64_t) row * heads + head) * D + c * 8);
     *reinterpret_cast<uint4*>(Qs + r * LDK + c * 8) = v;
   }
+  // a warp copies every fourth key of the tile, its lanes the 16-byte pieces of the entry: no divisions, one table
+  // lookup per key
   auto load_tile = [&](int tile, int buf) {
     const int j0 = tile * kKeyTile;
-    for (int e = tid; e < kKeyTile * CH; e += 128) {
-      const int jj = e / CH, c = e % CH, j = j0 + jj;
+    for (int jj = warp; jj < kKeyTile; jj += 4) {
+      const int j = j0 + jj;
       const bool ok = j <= pos;
-      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / page] * page + j % page) * D + c * 8 : pool;
-      cp_async16(Ks + (buf * kKeyTile + jj) * LDK + c * 8, src, ok ? 16 : 0);
+      const __nv_bfloat16* src = ok ? pool + (((int64_t) bt[j >> page_shift] << page_shift) + (j & page_mask)) * D : pool;
+      __nv_bfloat16* dst = Ks + (buf * kKeyTile + jj) * LDK;
+      for (int c = lane; c < CH; c += 32) cp_async16(dst + c * 8, ok ? src + c * 8 : src, ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -195,27 +211,51 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16
   if (t0 < t1) load_tile(t0, 0);
   for (int tile = t0; tile < t1; ++tile) {
     const int buf = (tile - t0) & 1;
-    if (tile + 1 < t1) {
-      load_tile(tile + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();        // this tile is in shared memory, and every warp is done with the previous one:
+    if (tile + 1 < t1) load_tile(tile + 1, buf ^ 1);      // its buffer, the P tile and the maxima can be written again
     const __nv_bfloat16* Kb = Ks + buf * kKeyTile * LDK;
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    float s[4];
     {
-      const __nv_bfloat16* qr = Qs + g * LDK + 2 * t;
-      const __nv_bfloat16* kr = Kb + (warp * 8 + g) * LDK + 2 * t;
-#pragma unroll 4
-      for (int kk = 0; kk < D; kk += 16) {
-        uint32_t a[4];
-        a[0] = *reinterpret_cast<const uint32_t*>(qr + kk);
-        a[1] = *reinterpret_cast<const uint32_t*>(qr + 8 * LDK + kk);
-        a[2] = *reinterpret_cast<const uint32_t*>(qr + kk + 8);
-        a[3] = *reinterpret_cast<const uint32_t*>(qr + 8 * LDK + kk + 8);
-        mma_bf16_16816(s, a, *reinterpret_cast<const uint32_t*>(kr + kk), *reinterpret_cast<const uint32_t*>(kr + kk + 8));
+      // four accumulators take the k steps in turn: a chain of D / 16 dependent MMAs would leave the tensor pipe idle
+      float sp[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sp[i][0] = sp[i][1] = sp[i][2] = sp[i][3] = 0.f;
+      // fragments come through ldmatrix: one instruction per 16 x 16 query block, one per two k steps of the keys.
+      // A block: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15); B: keys 8w..8w+7 x four runs of 8 k
+      const int mi = lane >> 3, r8 = lane & 7;
+      const uint32_t q_addr = (uint32_t) __cvta_generic_to_shared(Qs + (r8 + (mi & 1) * 8) * LDK + (mi >> 1) * 8);
+      const uint32_t k_addr = (uint32_t) __cvta_generic_to_shared(Kb + (warp * 8 + r8) * LDK + mi * 8);
+      int kk = 0;
+      for (; kk + 64 <= D; kk += 64) {
+        uint32_t a0[4], a1[4], a2[4], a3[4], b01[4], b23[4];
+        ldsm_x4(a0, q_addr + kk * 2);
+        ldsm_x4(a1, q_addr + (kk + 16) * 2);
+        ldsm_x4(a2, q_addr + (kk + 32) * 2);
+        ldsm_x4(a3, q_addr + (kk + 48) * 2);
+        ldsm_x4(b01, k_addr + kk * 2);
+        ldsm_x4(b23, k_addr + (kk + 32) * 2);
+        mma_bf16_16816(sp[0], a0, b01[0], b01[1]);
+        mma_bf16_16816(sp[1], a1, b01[2], b01[3]);
+        mma_bf16_16816(sp[2], a2, b23[0], b23[1]);
+        mma_bf16_16816(sp[3], a3, b23[2], b23[3]);
       }
+      for (; kk + 32 <= D; kk += 32) {
+        uint32_t a0[4], a1[4], b01[4];
+        ldsm_x4(a0, q_addr + kk * 2);
+        ldsm_x4(a1, q_addr + (kk + 16) * 2);
+        ldsm_x4(b01, k_addr + kk * 2);
+        mma_bf16_16816(sp[0], a0, b01[0], b01[1]);
+        mma_bf16_16816(sp[1], a1, b01[2], b01[3]);
+      }
+      if (kk < D) {          // one k step of 16 left (lanes 16-31 give valid, unused addresses)
+        uint32_t a0[4], b0, b1;
+        ldsm_x4(a0, q_addr + kk * 2);
+        ldsm_x2(b0, b1, (uint32_t) __cvta_generic_to_shared(Kb + (warp * 8 + r8) * LDK + (mi & 1) * 8) + kk * 2);
+        mma_bf16_16816(sp[2], a0, b0, b1);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] = (sp[0][i] + sp[1][i]) + (sp[2][i] + sp[3][i]);
     }
     const int j = tile * kKeyTile + warp * 8 + 2 * t;
     s[0] = j <= pos ? s[0] * scale : -INFINITY;
@@ -237,40 +277,51 @@ __global__ void __launch_bounds__(128) latent_attention_mma_kernel(__nv_bfloat16
     const __nv_bfloat162 p23 = __floats2bfloat162_rn(__expf(s[2] - mn1), __expf(s[3] - mn1));
     *reinterpret_cast<__nv_bfloat162*>(Ps + g * kPsLd + warp * 8 + 2 * t) = p01;
     *reinterpret_cast<__nv_bfloat162*>(Ps + (g + 8) * kPsLd + warp * 8 + 2 * t) = p23;
-    float ps0 = __bfloat162float(p01.x) + __bfloat162float(p01.y), ps1 = __bfloat162float(p23.x) + __bfloat162float(p23.y);
-    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 1);
-    ps0 += __shfl_xor_sync(0xffffffffu, ps0, 2);
-    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 1);
-    ps1 += __shfl_xor_sync(0xffffffffu, ps1, 2);
-    if (t == 0) { red[64 + warp * 16 + g] = ps0; red[64 + warp * 16 + g + 8] = ps1; }
-    __syncthreads();
+    // the row sums stay per thread (its two keys of the tile) until the end: every thread rescales by the same factor
     const float c0 = __expf(m0 - mn0), c1 = __expf(m1 - mn1);     // 0 on the first tile
-    float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) { sum0 += red[64 + w * 16 + g]; sum1 += red[64 + w * 16 + g + 8]; }
-    l0 = l0 * c0 + sum0;
-    l1 = l1 * c1 + sum1;
+    l0 = l0 * c0 + (__bfloat162float(p01.x) + __bfloat162float(p01.y));
+    l1 = l1 * c1 + (__bfloat162float(p23.x) + __bfloat162float(p23.y));
     m0 = mn0;
     m1 = mn1;
+    __syncthreads();        // the P tile is complete
 #pragma unroll
     for (int n = 0; n < NTO; ++n) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+    {
+      const int mi = lane >> 3, r8 = lane & 7;
+      const uint32_t p_addr = (uint32_t) __cvta_generic_to_shared(Ps + (r8 + (mi & 1) * 8) * kPsLd + (mi >> 1) * 8);
+      // V fragments: the key tile itself, transposed on the way in; one ldmatrix.x4 feeds two 8-column tiles
+      const uint32_t v_addr = (uint32_t) __cvta_generic_to_shared(Kb + (r8 + (mi & 1) * 8) * LDK + warp * (LAT / 4) + (mi >> 1) * 8);
 #pragma unroll
-    for (int kk = 0; kk < kKeyTile; kk += 16) {
-      uint32_t a[4];
-      a[0] = *reinterpret_cast<const uint32_t*>(Ps + g * kPsLd + kk + 2 * t);
-      a[1] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * kPsLd + kk + 2 * t);
-      a[2] = *reinterpret_cast<const uint32_t*>(Ps + g * kPsLd + kk + 2 * t + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(Ps + (g + 8) * kPsLd + kk + 2 * t + 8);
-      const uint32_t kaddr = (uint32_t) __cvta_generic_to_shared(Kb + (kk + (lane & 15)) * LDK + warp * (LAT / 4));
+      for (int kk = 0; kk < kKeyTile; kk += 16) {
+        uint32_t a[4];
+        ldsm_x4(a, p_addr + kk * 2);
+        const uint32_t vk = v_addr + kk * LDK * 2;
 #pragma unroll
-      for (int n = 0; n < NTO; ++n) {
-        uint32_t b0, b1;
-        asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(kaddr + n * 16));
-        mma_bf16_16816(o[n], a, b0, b1);
+        for (int n = 0; n + 1 < NTO; n += 2) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, vk + n * 16);
+          mma_bf16_16816(o[n], a, b[0], b[1]);
+          mma_bf16_16816(o[n + 1], a, b[2], b[3]);
+        }
+        if (NTO & 1) {
+          uint32_t b0, b1;
+          const uint32_t kaddr = (uint32_t) __cvta_generic_to_shared(Kb + (kk + (lane & 15)) * LDK + warp * (LAT / 4)) + (NTO - 1) * 16;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(kaddr));
+          mma_bf16_16816(o[NTO - 1], a, b0, b1);
+        }
       }
     }
-    __syncthreads();
   }
+  // row sums: over the four threads of a row group, then over the warps (each saw its own keys of every tile)
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();
+  if (t == 0) { red[64 + warp * 16 + g] = l0; red[64 + warp * 16 + g + 8] = l1; }
+  __syncthreads();
+  l0 = (red[64 + g] + red[64 + 16 + g]) + (red[64 + 32 + g] + red[64 + 48 + g]);
+  l1 = (red[64 + g + 8] + red[64 + 16 + g + 8]) + (red[64 + 32 + g + 8] + red[64 + 48 + g + 8]);
 
   const int h0 = hg * kTcHeads + g, h1 = h0 + 8;
   if (nsplit == 1) {
@@ -333,7 +384,11 @@ int launch_latent_mma(__nv_bfloat16* out, float* partial, const __nv_bfloat16* q
   const int D = NTO * 32 + rot_dim;
   const size_t smem = (size_t) (kTcHeads + 2 * kKeyTile) * (D + 8) * 2 + kTcHeads * kPsLd * 2 + 2 * 4 * 16 * sizeof(float);
   if (smem > 227 * 1024) return -2;
-  TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<NTO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+  static size_t raised = 48 * 1024;      // the opt-in only ever grows, and only outside a replayed region
+  if (smem > raised) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_mma_kernel<NTO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = smem;
+  }
   dim3 grid(rows, (heads + kTcHeads - 1) / kTcHeads, nsplit);
   latent_attention_mma_kernel<NTO><<<grid, 128, smem, s>>>(out, partial, qa, pool, tok_seq, tok_pos, block_table, max_blocks,
                                                            page, heads, rot_dim, scale, nsplit);
@@ -386,7 +441,7 @@ extern "C" int tb_latent_attention(void* out, const void* qa, const void* pool, 
     return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (rows == 0) return 0;
-  if (tb_latent_attention_tensor_cores(dtype, lat, rot_dim) && (uintptr_t) qa % 16 == 0 && (uintptr_t) pool % 16 == 0 &&
+  if (tb_latent_attention_tensor_cores(dtype, lat, rot_dim) && (page & (page - 1)) == 0 && (uintptr_t) qa % 16 == 0 && (uintptr_t) pool % 16 == 0 &&
       (uintptr_t) out % 4 == 0) {
     if (nsplit < 1 || !workspace) nsplit = 1;
     if (nsplit > 64) nsplit = 64;
@@ -407,14 +462,21 @@ extern "C" int tb_latent_attention(void* out, const void* qa, const void* pool, 
   if (smem > 227 * 1024) return -2;
   cudaStream_t s = (cudaStream_t) stream;
   dim3 grid(rows, (heads + kAttnWarps - 1) / kAttnWarps);
+  static size_t raised_f = 48 * 1024, raised_b = 48 * 1024;
   if (dtype == TB_DT_F32) {
-    TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    if (smem > raised_f) {
+      TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+      raised_f = smem;
+    }
     latent_attention_kernel<float><<<grid, kAttnWarps * 32, smem, s>>>((float*) out, (const float*) qa, (const float*) pool,
                                                                        tok_seq, tok_pos, block_table, max_blocks, page, heads,
                                                                        lat, rot_dim, scale);
   } else {
-    TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int) smem));
+    if (smem > raised_b) {
+      TB_CHECK_CUDA(cudaFuncSetAttribute(latent_attention_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int) smem));
+      raised_b = smem;
+    }
     latent_attention_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, smem, s>>>(
         (__nv_bfloat16*) out, (const __nv_bfloat16*) qa, (const __nv_bfloat16*) pool, tok_seq, tok_pos, block_table,
         max_blocks, page, heads, lat, rot_dim, scale);

@@ -211,16 +211,39 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
 
 // ---------------------------------------------------------------------------------------------------------------
 template <typename AT, typename CT, int MR>
-__global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p) {
+__global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p, int vec_a) {
   extern __shared__ __align__(16) __nv_bfloat16 a_s[];          // [MR][K]
   const int b = blockIdx.y;
   const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
   const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) b * p.w_bs;
   CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
   const int K = p.K;
-  for (int e = threadIdx.x; e < MR * K; e += 256) {
-    const int m = e / K, k = e - m * K;
-    a_s[e] = m < p.M ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) m * p.lda + k])) : __float2bfloat16_rn(0.f);
+  if (vec_a) {
+    // 8 elements per thread and trip, no divisions: the staging must stay small beside the weight rows a CTA streams
+    for (int m = 0; m < MR; ++m) {
+      for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+        __align__(16) __nv_bfloat16 v[8];
+        if (m < p.M) {
+          const AT* src = A + (int64_t) m * p.lda + k;
+          if constexpr (sizeof(AT) == 4) {
+            const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
+            v[0] = __float2bfloat16_rn(f0.x); v[1] = __float2bfloat16_rn(f0.y); v[2] = __float2bfloat16_rn(f0.z);
+            v[3] = __float2bfloat16_rn(f0.w); v[4] = __float2bfloat16_rn(f1.x); v[5] = __float2bfloat16_rn(f1.y);
+            v[6] = __float2bfloat16_rn(f1.z); v[7] = __float2bfloat16_rn(f1.w);
+          } else {
+            *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src);
+          }
+        } else {
+          *reinterpret_cast<uint4*>(v) = make_uint4(0, 0, 0, 0);
+        }
+        *reinterpret_cast<uint4*>(a_s + m * K + k) = *reinterpret_cast<const uint4*>(v);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < MR * K; e += 256) {
+      const int m = e / K, k = e - m * K;
+      a_s[e] = m < p.M ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) m * p.lda + k])) : __float2bfloat16_rn(0.f);
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -268,18 +291,26 @@ template <typename AT, typename CT>
 int launch_gemv(const LinArgs& p, int batch, cudaStream_t s) {
   const int mr = p.M <= 1 ? 1 : (p.M <= 2 ? 2 : (p.M <= 4 ? 4 : 8));
   const size_t smem = (size_t) mr * p.K * sizeof(__nv_bfloat16);
-  // enough CTAs to cover the chip a few times over, but no more warps than output columns
+  // as many CTAs as stay resident (shared memory and threads), but no more warps than output columns: every CTA pays
+  // for staging the rows once, so it should stream as many weight rows as the grid allows
   int ctas = (p.N + 7) / 8;
-  const int cap = std::max(1, 148 * 4 / batch);
+  const int resident = (int) std::min<size_t>(8, (220 * 1024) / std::max<size_t>(smem, 1024));
+  const int cap = std::max(1, 148 * std::max(1, resident) / batch);
   if (ctas > cap) ctas = cap;
   dim3 grid(ctas, batch);
+  const int asz = (int) sizeof(AT);
+  const int vec_a = ((uintptr_t) p.a % 16 == 0) && (p.lda * asz % 16 == 0) && (p.a_bs * asz % 16 == 0);
 #define TB_GEMV_CASE(MR)                                                                                             \
-  case MR:                                                                                                           \
-    if (smem > 48 * 1024)                                                                                            \
+  case MR: {                                                                                                         \
+    static size_t raised = 48 * 1024; /* the opt-in only ever grows, and only outside a replayed region */           \
+    if (smem > raised) {                                                                                             \
       TB_CHECK_CUDA(cudaFuncSetAttribute(linear_gemv_kernel<AT, CT, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          (int) smem));                                                               \
-    linear_gemv_kernel<AT, CT, MR><<<grid, 256, smem, s>>>(p);                                                       \
-    break;
+      raised = smem;                                                                                                 \
+    }                                                                                                                \
+    linear_gemv_kernel<AT, CT, MR><<<grid, 256, smem, s>>>(p, vec_a);                                                     \
+    break;                                                                                                           \
+  }
   switch (mr) { TB_GEMV_CASE(1) TB_GEMV_CASE(2) TB_GEMV_CASE(4) TB_GEMV_CASE(8) }
 #undef TB_GEMV_CASE
   return 0;
@@ -307,7 +338,7 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
   const bool gemv_ok = w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO && M <= 8 && K % 8 == 0 && (uintptr_t) w % 16 == 0 &&
-                       w_bs % 8 == 0 && (size_t) 8 * K * 2 <= 160 * 1024 && batch <= 65535;
+                       w_bs % 8 == 0 && (size_t) (M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8))) * K * 2 <= 200 * 1024 && batch <= 65535;
   if (gemv_ok) {
     int rc;
     if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, batch, s) : launch_gemv<float, __nv_bfloat16>(p, batch, s);

@@ -92,11 +92,11 @@ __global__ void rglru_scan_kernel(T* out, const float* u, const float* gates, co
 
 
 // Chunked form for long portions (prefill): the recurrence S_t = a_t S_(t-1) + b_t composes, so a sequence's rows are cut
-// into chunks of kScanChunk; (1) every (chunk, channel) scans its rows from zero and keeps the product of its a's and its
+// into chunks of kScanChunk rows; (1) every (chunk, channel) scans its rows from zero and keeps the product of its a's and its
 // final value, (2) one thread per (sequence, channel) walks the chunk summaries in order, leaves every chunk's incoming
 // state and the sequence's new state, (3) every (chunk, channel) scans again from its incoming state and writes S * y.
 // Gates are recomputed in (3) instead of stored: two transcendental passes cost less than 16 bytes per element of traffic.
-constexpr int kScanChunk = 64;
+constexpr int kScanChunk = 32;
 
 struct GateCoef { float a, b; };
 __device__ __forceinline__ GateCoef rglru_coef(float gr, float gi, float uv, float c_sp) {
@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(128) rglru_chunk_kernel(T* out, const float* u
   const int64_t g_r = (int64_t) (b * 2) * bw + j, g_i = g_r + bw;
   const int64_t slot = ((int64_t) e * max_chunks + chunk) * channels + ch, plane = (int64_t) gridDim.z * max_chunks * channels;
   float S = PHASE == 1 ? 0.f : ws[2 * plane + slot], P = 1.f;
+#pragma unroll 4
   for (int64_t row = seq_start[e] + r0; row < seq_start[e] + r1; ++row) {
     const GateCoef k = rglru_coef(gates[row * 2 * channels + g_r], gates[row * 2 * channels + g_i], u[row * channels + ch], c_sp);
     S = fmaf(k.a, S, k.b);

@@ -45,11 +45,19 @@ class StateSlotManager:
 class RaggedBatch:
     """Device-side description of one step (see include/trtllm_b200_ragged.h), uploaded as ONE int32 buffer."""
 
-    def __init__(self, entries, want_rows, device):
-        """entries: [(token ids, past length, state slot, block ids)]; want_rows: row indices whose logits are wanted."""
-        tok_ids, tok_seq, tok_pos, start, length, past, slot = [], [], [], [], [], [], []
-        self.max_blocks = max(1, max(len(e[3]) for e in entries))
-        table = []
+    def __init__(self, entries, want_rows, device, max_blocks=None):
+        """entries: [(token ids, past length, state slot, block ids)]; want_rows: row indices whose logits are wanted.
+        ``max_blocks`` pads the block table's row length (a replayed step graph needs it fixed)."""
+        self.device = device
+        self.max_blocks = max(1, max(len(e[3]) for e in entries), max_blocks or 0)
+        host = self._pack(entries, want_rows)
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        self._host, self._dev = host, host.to(device, non_blocking=True)
+        self._views()
+
+    def _pack(self, entries, want_rows):
+        tok_ids, tok_seq, tok_pos, start, length, past, slot, table = [], [], [], [], [], [], [], []
         for i, (toks, p, s, blocks) in enumerate(entries):
             start.append(len(tok_ids))
             length.append(len(toks))
@@ -60,19 +68,27 @@ class RaggedBatch:
             tok_pos += range(p, p + len(toks))
             table += list(blocks) + [-1] * (self.max_blocks - len(blocks))
         self.num_rows, self.num_seqs, self.num_want = len(tok_ids), len(entries), len(want_rows)
-        self.max_len = max(length)        # ... and by the longest portion
-        self.max_pos = max(tok_pos)       # host-side hint for kernels that size their grids by context length
-        parts = [tok_ids, tok_seq, tok_pos, start, length, past, slot, table, list(want_rows)]
-        host = torch.tensor([v for p in parts for v in p], dtype=torch.int32)
-        if torch.device(device).type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(device, non_blocking=True)
-        self._host, self._dev, off, views = host, dev, 0, []
-        for p in parts:
-            views.append(dev[off:off + len(p)])
-            off += len(p)
+        self.max_len = max(length)        # host-side hints for kernels that size their grids by the longest portion
+        self.max_pos = max(tok_pos)       # ... and by context length
+        self._sizes = [len(tok_ids)] * 3 + [len(entries)] * 4 + [len(table), len(want_rows)]
+        return torch.tensor(tok_ids + tok_seq + tok_pos + start + length + past + slot + table + list(want_rows), dtype=torch.int32)
+
+    def _views(self):
+        off, views = 0, []
+        for n in self._sizes:
+            views.append(self._dev[off:off + n])
+            off += n
         (self.tok_ids, self.tok_seq, self.tok_pos, self.seq_start, self.seq_len, self.seq_past, self.seq_slot,
          self.block_table, self.want_rows) = views
+
+    def refill(self, entries, want_rows):
+        """Same shape, new contents, SAME device addresses (the batch a captured step graph reads)."""
+        sizes = self._sizes
+        host = self._pack(entries, want_rows)
+        if self._sizes != sizes:
+            raise ValueError("refill() needs a batch of the same shape")
+        self._host = host.pin_memory() if torch.device(self.device).type == "cuda" else host
+        self._dev.copy_(self._host, non_blocking=True)
 
 
 class StepContext:
@@ -100,8 +116,11 @@ class InflightSession:
     """Serves one ``LayerStackModel``.  ``max_tokens`` sizes the latent-cache pools (positions held by all live
     sequences together, each rounded up to whole pages); ``max_seqs`` is the number of state slots."""
 
-    def __init__(self, model, max_tokens: int, max_seqs: int = 4, tokens_per_block: int = 64, device="cuda"):
+    def __init__(self, model, max_tokens: int, max_seqs: int = 4, tokens_per_block: int = 64, device="cuda",
+                 use_cuda_graph: bool = True):
         self.model, self.device, self.page = model, torch.device(device), int(tokens_per_block)
+        self.use_cuda_graph = bool(use_cuda_graph) and self.device.type == "cuda"
+        self._graphs = {}
         blocks = max(1, -(-int(max_tokens) // self.page))
         self.kv_cache_manager = KVCacheManager(blocks=blocks, tokens_per_block=self.page, max_blocks_per_seq=blocks)
         self.slot_manager = StateSlotManager(max_seqs)
@@ -153,13 +172,52 @@ class InflightSession:
             for seq_id in fresh:          # nothing ran: a step that cannot be placed leaves no half-admitted sequence
                 self.end(seq_id)
             raise
-        batch = RaggedBatch(rows, want_rows, self.device)
-        ctx = StepContext(batch, self.pools, self.states, self.page)
-        x = self.model.forward(ctx, on_layer=on_layer)
+        if (self.use_cuda_graph and on_layer is None and len(want_rows) == n
+                and all(len(r[0]) == 1 for r in rows)):
+            logits = self._generation_step_graph(rows)
+        else:
+            batch = RaggedBatch(rows, want_rows, self.device)
+            ctx = StepContext(batch, self.pools, self.states, self.page)
+            x = self.model.forward(ctx, on_layer=on_layer)
+            self.last_batch = batch       # keeps the pinned upload buffer alive until the next step
+            logits = self.model.logits(x, batch.want_rows) if want_rows else None
         for seq_id, tokens, _ in entries:
             self.live[seq_id].length += len(tokens)
-        self.last_batch = batch           # keeps the pinned upload buffer alive until the next step
-        return self.model.logits(x, batch.want_rows) if want_rows else None
+        return logits
+
+    def _generation_step_graph(self, rows):
+        """A step in which every sequence brings ONE token and wants its logits (a generation step) is launch-bound:
+        ~20 kernels per layer against a few hundred microseconds of work.  Such steps are captured once per (number of
+        sequences, block-table width) as a CUDA graph over a batch description at fixed device addresses and replayed
+        with new contents; everything else of the step (positions, pages, slots) is data the kernels read."""
+        B = len(rows)
+        width = -(-max(len(r[3]) for r in rows) // 8) * 8
+        key = (B, width)
+        want = list(range(B))
+        g = self._graphs.get(key)
+        if g is None:
+            batch = RaggedBatch(rows, want, self.device, max_blocks=width)
+            batch.max_pos = width * self.page - 1            # sizes the key split for every length this table holds
+            ctx = StepContext(batch, self.pools, self.states, self.page)
+            logits = self.model.logits(self.model.forward(ctx), batch.want_rows)      # this step, eagerly
+            out = logits.clone()
+            graph, captured = torch.cuda.CUDAGraph(), None
+            try:
+                with torch.cuda.graph(graph):             # records, does not run: states and caches are not touched
+                    cctx = StepContext(batch, self.pools, self.states, self.page)
+                    captured = self.model.logits(self.model.forward(cctx), batch.want_rows)
+            except RuntimeError:
+                self.use_cuda_graph = False                   # capture not possible here: stay with eager launches
+                return out
+            if len(self._graphs) >= 32:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = (graph, batch, captured)
+            return out
+        graph, batch, captured = g
+        batch.refill(rows, want)
+        batch.max_pos = width * self.page - 1
+        graph.replay()
+        return captured.clone()
 
     # -- generation ------------------------------------------------------------------------------------------------
     def generate(self, prompts, max_new_tokens: int, sampling_config: SamplingConfig = None, max_step_tokens: int = 512):

@@ -74,7 +74,9 @@ class OpTimer:
             o = kw.get("out", out)
             B = w.shape[0] if w.dim() == 3 else 1
             N, K = w.shape[-2], w.shape[-1]
-            return "linear", 2.0 * a.shape[0] * N * K * B, nb(w) + a.shape[0] * B * K * a.element_size() + nb(o)
+            kind = "fp32-fma" if kw.get("compute", 0) else ("batched" if B > 1 else "dense")
+            return f"linear {kind} {a.shape[0]}x{N}x{K}" + (f"x{B}" if B > 1 else ""), 2.0 * a.shape[0] * N * K * B, \
+                nb(w) + a.shape[0] * B * K * a.element_size() + nb(o)
         if name == "latent_attention":
             qa, pool, batch = args[0], args[1], args[2]
             heads, lat, rot = args[4], args[5], args[6]
@@ -189,9 +191,12 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
     t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
     res["decode_tokens_per_s"] = round(B / t, 1)
     res["decode_ms_per_step"] = round(t * 1e3, 3)
+    sess.use_cuda_graph = False          # the operators are timed one by one on eager launches
     with OpTimer(torch, ops) as ot:
         sess.step(dec)
     res["decode_ops"] = ot.summary(peaks)
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_ms_per_step_eager"] = round(t * 1e3, 3)
     del sess, model
     torch.cuda.empty_cache()
 
@@ -243,6 +248,32 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
     like["attention_decode"] = {"us": round(t * 1e6, 1),
                                 "of_roofline": round(B * 2 * H * S * 128 * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     res["llama_like_kernels"] = like
+    del x, xd, qkv, kvc, qd
+    # this design's kernels alone on the same problem sizes (bf16)
+    own = {}
+    xb = torch.randn(S, L["hidden"], device="cuda").bfloat16()
+    wb = (torch.randn(w.shape[0], w.shape[1], device="cuda") * 0.02).bfloat16()
+    t = _time(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
+    own["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    xf = torch.randn(B, L["hidden"], device="cuda")
+    t = _time(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
+    own["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(wb.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    from .inflight import RaggedBatch
+    lat, rot, Hh, page = s["kv_rank"], s["rot_dim"], s["heads"], 64
+    nblk = -(-S // page)
+    pool = torch.randn((B * nblk * page, lat + rot), device="cuda").bfloat16()
+    pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
+    qa = torch.randn(S, Hh, lat + rot, device="cuda").bfloat16()
+    t = _time(torch, lambda: ops.latent_attention(qa, pool, pb, page, Hh, lat, rot, 0.07), steps, warmup, flush)
+    fl_a = 2.0 * (S * (S + 1) / 2) * Hh * (2 * lat + rot)
+    own["attention_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl_a / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
+    qd2 = qa[:B].contiguous()
+    t = _time(torch, lambda: ops.latent_attention(qd2, pool, db, page, Hh, lat, rot, 0.07), steps, warmup, flush)
+    own["attention_decode"] = {"us": round(t * 1e6, 1),
+                               "of_roofline": round(B * S * (lat + rot) * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3),
+                               "cache_bytes": B * S * (lat + rot) * 2, "llama_cache_bytes": B * 2 * H * S * 128 * 2}
+    res["zobasun_like_kernels"] = own
     res["peaks"] = peaks
     del ls, lt
     torch.cuda.empty_cache()

@@ -476,7 +476,7 @@ def latent_attention(qa, pool, batch, page, heads, lat, rot_dim, scale):
     nsplit, ws = 1, None
     if _rl.tb_latent_attention_tensor_cores(_dt(pool), lat, rot_dim):
         ctas = rows * -(-heads // 16)
-        nsplit = max(1, min(32, 296 // ctas, (batch.max_pos + 1) // 128))
+        nsplit = max(1, min(64, 296 // ctas, (batch.max_pos + 1) // 64))     # at least two key blocks per CTA
         if nsplit > 1:
             ws = torch.empty((rows * heads * nsplit * (lat + 2),), dtype=torch.float32, device=qa.device)
     check(_rl.tb_latent_attention(_p(out), _p(qa), _p(pool), _dt(pool), _p(batch.tok_seq), _p(batch.tok_pos),
@@ -503,8 +503,8 @@ def rglru_scan(u, gates, lam, y, state, batch, blocks, c):
     _chk_cuda(u, gates, lam, y, state)
     out = torch.empty_like(y)
     ws = None
-    if batch.max_len > 64:          # long portions: parallel chunks of 64 rows, summaries carried in order
-        ws = torch.empty((3 * batch.num_seqs * -(-batch.max_len // 64) * u.shape[1],), dtype=torch.float32, device=u.device)
+    if batch.max_len > 32:          # long portions: parallel chunks of 32 rows, summaries carried in order
+        ws = torch.empty((3 * batch.num_seqs * -(-batch.max_len // 32) * u.shape[1],), dtype=torch.float32, device=u.device)
     check(_rl.tb_rglru_scan(_p(out), _dt(out), _p(u), _p(gates), _p(lam), _dt(lam), _p(y), _p(state), _p(batch.seq_start),
                             _p(batch.seq_len), _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, u.shape[1], blocks,
                             float(c), batch.max_len, _p(ws), _stream()), "tb_rglru_scan")
