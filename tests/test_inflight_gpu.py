@@ -214,6 +214,45 @@ def test_one_key_stands_out(dtype, where):
                 _close(got[r, 1], entries[target, :lat], dtype, f"spike at {target} seen from {p}", scale=8.0)
 
 
+@pytest.mark.parametrize("lat,rot,heads", [(32, 16, 1), (96, 32, 5), (128, 16, 20), (160, 16, 16), (192, 64, 3), (256, 16, 17),
+                                          (384, 32, 2), (512, 64, 16), (512, 64, 33), (40, 6, 3), (64, 8, 4)])
+def test_latent_attention_operator_sizes(lat, rot, heads):
+    """Every latent width the tensor-core kernel is instantiated for (and two it is not), more heads than one CTA
+    takes, a prompt portion and single rows whose keys are dealt to several CTAs, over shuffled pages."""
+    from trtllm_llama_b200 import ops
+    from trtllm_llama_b200.inflight import RaggedBatch
+    dtype, page, D = torch.bfloat16, 16, lat + rot
+    g = torch.Generator().manual_seed(lat + heads)
+    lens = [300, 70]
+    nblk = [-(-n // page) for n in lens]
+    perm = torch.randperm(sum(nblk) + 3, generator=g).tolist()
+    blocks = [perm[:nblk[0]], perm[nblk[0]:nblk[0] + nblk[1]]]
+    entries = [torch.randn(n, D, generator=g).to(dtype) for n in lens]
+    pool = torch.full(((sum(nblk) + 3) * page, D), float("nan"), dtype=dtype)
+    for e, b in zip(entries, blocks):
+        for j in range(e.shape[0]):
+            pool[b[j // page] * page + j % page] = e[j]
+    pool = pool.cuda()
+
+    def want(q, e, p):           # q [H, D] at position p of a sequence whose entries are e
+        vis = e[: p + 1].double()
+        return torch.softmax(q.double() @ vis.T * 0.3, -1) @ vis[:, :lat]
+
+    # a portion of 40 rows at the end of the first sequence beside the whole second sequence
+    rows = [([0] * 40, lens[0] - 40, 0, blocks[0]), ([0] * lens[1], 0, 1, blocks[1])]
+    qa = (torch.randn(40 + lens[1], heads, D, generator=g) * 0.5).to(dtype)
+    got = ops.latent_attention(qa.cuda(), pool, RaggedBatch(rows, [], "cuda"), page, heads, lat, rot, 0.3)
+    ref = torch.stack([want(qa[r], entries[0], lens[0] - 40 + r) for r in range(40)] +
+                      [want(qa[40 + r], entries[1], r) for r in range(lens[1])])
+    _close(got, ref, dtype, f"prompt rows, latent {lat} rot {rot} heads {heads}")
+    # single rows at the last positions: long enough for the keys to be split over CTAs
+    rows = [([0], lens[0] - 1, 0, blocks[0]), ([0], lens[1] - 1, 1, blocks[1])]
+    qd = (torch.randn(2, heads, D, generator=g) * 0.5).to(dtype)
+    got = ops.latent_attention(qd.cuda(), pool, RaggedBatch(rows, [], "cuda"), page, heads, lat, rot, 0.3)
+    ref = torch.stack([want(qd[0], entries[0], lens[0] - 1), want(qd[1], entries[1], lens[1] - 1)])
+    _close(got, ref, dtype, f"single rows, latent {lat} rot {rot} heads {heads}")
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # whole models through the session
 # ---------------------------------------------------------------------------------------------------------------
@@ -322,6 +361,25 @@ def test_greedy_generation_through_the_scheduler(dtype):
             best = lg[i].topk(2)
             if int(best.indices[0]) != tok:
                 assert float(best.values[0] - lg[i][tok]) <= 2 * TOL[dtype] * float(lg.abs().max()), f"step {i}: id {tok} is not the arg-max"
+
+
+def test_sampled_generation_uses_the_sampling_kernel():
+    """top-k sampling through the scheduler: reproducible for a seed, different for another, and every id is one of the
+    oracle's k best on the same history (or within tolerance of the k-th)."""
+    from trtllm_llama_b200.runtime import SamplingConfig
+    cfg, t, model = _model("odd", torch.float32, seed=5)
+    prompts = [_tokens(n, cfg["vocab"], 60 + n) for n in (7, 21)]
+    sess = _session(model, max_tokens=16 * 8, max_seqs=2, page=16)
+    sc = SamplingConfig(end_id=None, top_k=4, top_p=0.0, temperature=0.8, random_seed=11)
+    a = sess.generate(prompts, 10, sc, max_step_tokens=16)
+    b = sess.generate(prompts, 10, sc, max_step_tokens=16)
+    c = sess.generate(prompts, 10, SamplingConfig(end_id=None, top_k=4, top_p=0.0, temperature=0.8, random_seed=12), max_step_tokens=16)
+    assert a == b and a != c
+    for p, o in zip(prompts, a):
+        lg = O.zobasun_forward(cfg, t, p + o[:-1])[len(p) - 1:]
+        for i, tok in enumerate(o):
+            kth = lg[i].topk(4).values[-1]
+            assert lg[i][tok] >= kth - 2 * TOL[torch.float32] * float(lg.abs().max()), f"step {i}: id {tok} is outside the top 4"
 
 
 def test_registry_loads_a_checkpoint_folder(tmp_path):
