@@ -27,7 +27,7 @@ enum { TB_DT_F32 = 1, TB_DT_BF16 = 2 };
 enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1 };
 /* tb_linear compute paths: AUTO = tensor cores for bf16 weights, FMA for fp32 weights; FMA32 = fp32 multiply-add in a
  * fixed k order whatever the storage type (the all-32-bit mode, and the small products that feed a recurrence). */
-enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1 };
+enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1, TB_COMPUTE_TILES = 2 /* bf16: the warp-MMA tiles at any row count (A/B) */ };
 
 /* C[b][m, n] = act( sum_k A[b][m, k] * W[b][n, k] + bias[b][n] ),  b < batch.
  * A: a_dtype, row stride lda, batch stride a_bs (elements).  W: w_dtype, [N, K] rows contiguous, batch stride w_bs.
@@ -86,7 +86,7 @@ int tb_latent_kv_append(void* pool, int dtype, const float* kv, int64_t ldkv, co
  * bf16 with 32 | lat, 16 | rot_dim runs on tensor cores (tb_latent_attention_tensor_cores tells): one CTA per (row,
  * 16 heads, key range).  nsplit > 1 deals every row's key blocks to nsplit CTAs whose partial results (workspace: fp32
  * [rows, heads, nsplit, lat + 2]) a second kernel merges — for steps with few rows and long contexts; other
- * configurations ignore it. */
+ * configurations ignore it; nsplit < 0 keeps any configuration on the warp-per-head kernel (A/B). */
 int tb_latent_attention_tensor_cores(int dtype, int lat, int rot_dim);
 int tb_latent_attention(void* out, const void* qa, const void* pool, int dtype, const int* tok_seq, const int* tok_pos,
                         const int* block_table, int max_blocks, int page, int rows, int heads, int lat, int rot_dim,

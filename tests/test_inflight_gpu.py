@@ -245,6 +245,14 @@ def test_latent_attention_operator_sizes(lat, rot, heads):
     ref = torch.stack([want(qa[r], entries[0], lens[0] - 40 + r) for r in range(40)] +
                       [want(qa[40 + r], entries[1], r) for r in range(lens[1])])
     _close(got, ref, dtype, f"prompt rows, latent {lat} rot {rot} heads {heads}")
+    # the tensor-core kernel against the warp-per-head kernel on the same operands: only the bf16 rounding of the
+    # probabilities and of the outputs may differ
+    ops.FORCE_SIMT_ATTENTION = True
+    try:
+        plain = ops.latent_attention(qa.cuda(), pool, RaggedBatch(rows, [], "cuda"), page, heads, lat, rot, 0.3)
+    finally:
+        ops.FORCE_SIMT_ATTENTION = False
+    assert (got.float() - plain.float()).abs().max() <= 1.2e-2 * ref.abs().max(), "the two attention kernels disagree"
     # single rows at the last positions: long enough for the keys to be split over CTAs
     rows = [([0], lens[0] - 1, 0, blocks[0]), ([0], lens[1] - 1, 1, blocks[1])]
     qd = (torch.randn(2, heads, D, generator=g) * 0.5).to(dtype)

@@ -441,7 +441,7 @@ extern "C" int tb_latent_attention(void* out, const void* qa, const void* pool, 
     return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (rows == 0) return 0;
-  if (tb_latent_attention_tensor_cores(dtype, lat, rot_dim) && (page & (page - 1)) == 0 && (uintptr_t) qa % 16 == 0 && (uintptr_t) pool % 16 == 0 &&
+  if (nsplit >= 0 && tb_latent_attention_tensor_cores(dtype, lat, rot_dim) && (page & (page - 1)) == 0 && (uintptr_t) qa % 16 == 0 && (uintptr_t) pool % 16 == 0 &&
       (uintptr_t) out % 4 == 0) {
     if (nsplit < 1 || !workspace) nsplit = 1;
     if (nsplit > 64) nsplit = 64;

@@ -337,6 +337,7 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
   LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
+  if (compute == TB_COMPUTE_TILES && w_dtype != TB_DT_BF16) compute = TB_COMPUTE_AUTO;
   const bool gemv_ok = w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO && M <= 8 && K % 8 == 0 && (uintptr_t) w % 16 == 0 &&
                        w_bs % 8 == 0 && (size_t) (M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8))) * K * 2 <= 200 * 1024 && batch <= 65535;
   if (gemv_ok) {
@@ -344,7 +345,7 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
     if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, batch, s) : launch_gemv<float, __nv_bfloat16>(p, batch, s);
     else rc = c_dtype == TB_DT_F32 ? launch_gemv<__nv_bfloat16, float>(p, batch, s) : launch_gemv<__nv_bfloat16, __nv_bfloat16>(p, batch, s);
     if (rc) return rc;
-  } else if (w_dtype == TB_DT_BF16 && compute == TB_COMPUTE_AUTO) {
+  } else if (w_dtype == TB_DT_BF16 && (compute == TB_COMPUTE_AUTO || compute == TB_COMPUTE_TILES)) {
     const int asz = a_dtype == TB_DT_F32 ? 4 : 2;
     const int vec_a = ((uintptr_t) a % 16 == 0) && (lda * asz % 16 == 0) && (a_bs * asz % 16 == 0);
     const int vec_w = ((uintptr_t) w % 16 == 0) && (K % 8 == 0) && (w_bs % 8 == 0);

@@ -347,6 +347,11 @@ ACT_NONE, ACT_GELU_TANH = 0, 1
 COMPUTE_AUTO, COMPUTE_FMA32 = 0, 1
 # rows from which a bf16 projection goes to the tcgen05 kernel; below, the streaming GEMV (<= 8 rows) or the warp-MMA tiles
 TC_MIN_ROWS = 17
+# A/B switches (tests and measurements): keep bf16 attention on the warp-per-head kernel / bf16 projections of few rows on
+# the tile kernel instead of the streaming GEMV
+FORCE_SIMT_ATTENTION = False
+FORCE_TILE_LINEAR = False
+COMPUTE_TILES = 2
 
 
 def _dt(t):
@@ -400,6 +405,8 @@ def linear(a, w, bias=None, out=None, out_dtype=None, act=ACT_NONE, compute=COMP
         check(_rl.tb_gemm_tc_bf16(_p(out), 1 if out.dtype == torch.float32 else 3, _p(a), _p(w), _p(bias), act, M, N, K,
                                   _p(ws), ws.numel(), _p(_counters(a.device)), _stream()), "tb_gemm_tc_bf16")
         return out
+    if FORCE_TILE_LINEAR and compute == COMPUTE_AUTO:
+        compute = COMPUTE_TILES
     check(_rl.tb_linear(_p(out), _dt(out), ldc, c_bs, _p(a), _dt(a), lda, a_bs, _p(w), _dt(w), w_bs, _p(bias), b_bs,
                         M, N, K, B, act, compute, _stream()), "tb_linear")
     return out
@@ -474,7 +481,9 @@ def latent_attention(qa, pool, batch, page, heads, lat, rot_dim, scale):
     rows = qa.shape[0]
     out = torch.empty((rows, heads, lat), dtype=qa.dtype, device=qa.device)
     nsplit, ws = 1, None
-    if _rl.tb_latent_attention_tensor_cores(_dt(pool), lat, rot_dim):
+    if FORCE_SIMT_ATTENTION:
+        nsplit = -1
+    elif _rl.tb_latent_attention_tensor_cores(_dt(pool), lat, rot_dim):
         ctas = rows * -(-heads // 16)
         nsplit = max(1, min(64, 296 // ctas, (batch.max_pos + 1) // 64))     # at least two key blocks per CTA
         if nsplit > 1:
