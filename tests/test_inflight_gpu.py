@@ -33,6 +33,9 @@ STACKS = {
     "odd": dict(layers=[ATT, dict(REC, mlp=(50, 1.5)), dict(ATT, kv_from=0, mlp=(50, 1.5)), REC], width=40, vocab=61),
     "tc": dict(layers=[dict(REC, width=64, blocks=1, conv=2, mlp=(64, 3.0)), ATT_TC, dict(ATT_TC, kv_from=1), ATT_TC,
                        dict(ATT_TC, kv_from=1, mlp=None)], width=64, vocab=130, embed_scale=1.0),
+    # 64 | latent and 32 | latent + rot: the eight-warp form of the tensor-core attention
+    "tc8": dict(layers=[dict(ATT_TC, rot_dim=32, mlp=None), dict(type="rglru", width=32, blocks=2, conv=3, mlp=(48, 4.0)),
+                        dict(ATT_TC, rot_dim=32, kv_from=0)], width=48, vocab=77, embed_scale=2.0),
     "wide": dict(layers=[dict(type="latent_attention", heads=18, dim=8, rot_dim=8, vdim=8, kv_rank=96, q_rank=16, mlp=None),
                          dict(type="rglru", width=80, blocks=5, conv=5, mlp=None)], width=32, vocab=40, eps=1e-6),
 }
@@ -296,7 +299,7 @@ def test_portions(dtype, cuts):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["odd", "tc"])
+@pytest.mark.parametrize("name", ["odd", "tc", "tc8"])
 def test_mixed_batches_and_reuse(dtype, name):
     """Five requests of unequal length through FOUR slots and a pool that cannot hold them all at once: portions beside
     single tokens, requests that sit a step out, pages and slots handed on — every logit equals the request run alone."""
