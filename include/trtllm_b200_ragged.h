@@ -24,7 +24,7 @@ extern "C" {
 #endif
 
 enum { TB_DT_F32 = 1, TB_DT_BF16 = 2 };
-enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1 };
+enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1, TB_ACT_GATED = 2 /* tb_linear_gated only */ };
 /* tb_linear compute paths: AUTO = tensor cores for bf16 weights, FMA for fp32 weights; FMA32 = fp32 multiply-add in a
  * fixed k order whatever the storage type (the all-32-bit mode, and the small products that feed a recurrence). */
 enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1, TB_COMPUTE_TILES = 2 /* bf16: the warp-MMA tiles at any row count (A/B) */ };
@@ -36,6 +36,13 @@ enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1, TB_COMPUTE_TILES = 2 /* bf16: 
 int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const void* a, int a_dtype, int64_t lda, int64_t a_bs,
               const void* w, int w_dtype, int64_t w_bs, const void* bias, int64_t bias_bs, int M, int N, int K, int batch,
               int act, int compute, tb_stream_t stream);
+
+/* Gated feed-forward input side in one kernel, for generation steps (<= 8 rows, bf16 weights, 8 | K):
+ * out[m, j] = g * sigmoid(alpha * g) * (u + up_shift), g = min(a[m] . w[j], limit), u = clamp(a[m] . w[ff + j], -limit, limit),
+ * w [2 ff, K] = gate rows, then up rows.  Returns -3 when the shape is not one the streaming kernel takes; the caller
+ * then runs tb_linear + tb_gated_act, which compute the same. */
+int tb_linear_gated(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
+                    int M, int ff, int K, float alpha, float limit, float up_shift, tb_stream_t stream);
 
 /* Prompt-sized products of bf16 operands on the 5th-generation tensor cores (tcgen05 / TMEM / TMA, the kernel of
  * tb_gemm_tc with bf16 formats): c = act(x w^T + bias); x [M, K], w [N, K] bf16 contiguous, 8 | K, both 16-byte aligned;

@@ -118,6 +118,27 @@ def test_rmsnorm_and_activation():
     _close(got, gg * torch.sigmoid(1.702 * gg) * (uu + 1.0), torch.float32, "clamped gated activation")
 
 
+@pytest.mark.parametrize("rows", [1, 3, 8, 9])
+def test_gated_projection_fused_for_few_rows(rows):
+    """Up to 8 rows the gate / up projection and the clamped gated activation run as one streaming kernel; it must
+    equal the two-kernel form (which larger steps use) and the plain formula."""
+    from trtllm_llama_b200 import ops
+    g = torch.Generator().manual_seed(rows)
+    K, ff = 72, 50
+    x = torch.randn(rows, K, generator=g)
+    w = (torch.randn(2 * ff, K, generator=g) * 0.4).to(torch.bfloat16)
+    fused = ops.linear_gated(x.cuda(), w.cuda(), torch.float32, 1.702, 1.5, 1.0)
+    two = ops.gated_act(ops.linear(x.cuda(), w.cuda(), out_dtype=torch.float32), torch.float32, 1.702, 1.5, 1.0)
+    xb = x.to(torch.bfloat16).double()
+    gg, uu = (xb @ w[:ff].double().T).clamp(max=1.5), (xb @ w[ff:].double().T).clamp(-1.5, 1.5)
+    want = gg * torch.sigmoid(1.702 * gg) * (uu + 1.0)
+    _close(two, want, torch.float32, "projection + activation")
+    if rows <= 8:
+        _close(fused, want, torch.float32, "fused gated projection")
+    else:
+        assert fused is None
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # mixers alone, driven through the session's batch description
 # ---------------------------------------------------------------------------------------------------------------

@@ -182,6 +182,7 @@ SIGNATURES.update({
 f64 = C.c_double
 RAGGED_SIGNATURES = {
     "tb_linear": (i32, [vp, i32, i64, i64, vp, i32, i64, i64, vp, i32, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_linear_gated": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, i32, i32, i32, f32, f32, f32, vp]),
     "tb_gemm_tc_bf16": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp]),
     "tb_cast_rows_bf16": (i32, [vp, vp, i64, i32, i32, vp]),
     "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),

@@ -38,6 +38,7 @@ struct LinArgs {
   void* c; const void* a; const void* w; const void* bias;
   int64_t ldc, c_bs, lda, a_bs, w_bs, bias_bs;
   int M, N, K, act;
+  float alpha, limit, up_shift;      // TB_ACT_GATED (GEMV only): W holds N gate rows, then N up rows
 };
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -253,6 +254,45 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p, int vec_a) 
     float acc[MR];
 #pragma unroll
     for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+    if (p.act == TB_ACT_GATED) {
+      // gated feed-forward: the warp streams gate row n and up row n + N together and applies the activation itself,
+      // so the [M, 2 N] intermediate never exists
+      const __nv_bfloat16* ur = wr + (int64_t) p.N * K;
+      float up[MR];
+#pragma unroll
+      for (int m = 0; m < MR; ++m) up[m] = 0.f;
+#pragma unroll 2
+      for (int k = lane * 8; k < K; k += 256) {
+        const uint4 gv = __ldg(reinterpret_cast<const uint4*>(wr + k)), uv = __ldg(reinterpret_cast<const uint4*>(ur + k));
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+          const uint4 av = *reinterpret_cast<const uint4*>(a_s + m * K + k);
+          const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(a2[j]), gw = __bfloat1622float2(g2[j]), uw = __bfloat1622float2(u2[j]);
+            acc[m] = fmaf(gw.x, f.x, acc[m]);
+            acc[m] = fmaf(gw.y, f.y, acc[m]);
+            up[m] = fmaf(uw.x, f.x, up[m]);
+            up[m] = fmaf(uw.y, f.y, up[m]);
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MR; ++m) { acc[m] = warp_sum(acc[m]); up[m] = warp_sum(up[m]); }
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+          if (m >= p.M) break;
+          float gq = acc[m], uq = up[m];
+          if (p.limit > 0.f) { gq = fminf(gq, p.limit); uq = fminf(fmaxf(uq, -p.limit), p.limit); }
+          C[(int64_t) m * p.ldc + n] = from_f<CT>(gq * (1.f / (1.f + expf(-p.alpha * gq))) * (uq + p.up_shift));
+        }
+      }
+      continue;
+    }
 #pragma unroll 4
     for (int k = lane * 8; k < K; k += 256) {
       const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr + k));
@@ -334,7 +374,8 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
   if (!c || !a || !w || !ok(c_dtype) || !ok(a_dtype) || !ok(w_dtype) || N <= 0 || K <= 0 || batch <= 0 || M < 0) return -1;
   if (M == 0) return 0;
   if (batch > 65535 || (M + 63) / 64 > 65535) return -2;
-  LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act};
+  if (act == TB_ACT_GATED) return -1;      // tb_linear_gated
+  LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act, 0.f, 0.f, 0.f};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
   if (compute == TB_COMPUTE_TILES && w_dtype != TB_DT_BF16) compute = TB_COMPUTE_AUTO;
@@ -363,6 +404,26 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
     if (a_dtype == TB_DT_F32) launch_fma<float, float>(p, c_dtype, grid, s);
     else launch_fma<__nv_bfloat16, float>(p, c_dtype, grid, s);
   }
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_linear_gated(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w,
+                               int w_dtype, int M, int ff, int K, float alpha, float limit, float up_shift,
+                               tb_stream_t stream) {
+  using namespace tb;
+  if (!c || !a || !w || ff <= 0 || K <= 0 || M < 0) return -1;
+  if ((c_dtype != TB_DT_F32 && c_dtype != TB_DT_BF16) || (a_dtype != TB_DT_F32 && a_dtype != TB_DT_BF16)) return -1;
+  if (M == 0) return 0;
+  // the fused form exists for the streaming kernel only: the caller runs projection + activation otherwise
+  const int mr = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
+  if (w_dtype != TB_DT_BF16 || M > 8 || K % 8 || (uintptr_t) w % 16 || (size_t) mr * K * 2 > 200 * 1024) return -3;
+  LinArgs p{c, a, w, nullptr, ldc, 0, lda, 0, 0, 0, M, ff, K, TB_ACT_GATED, alpha, limit, up_shift};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc;
+  if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, 1, s) : launch_gemv<float, __nv_bfloat16>(p, 1, s);
+  else rc = c_dtype == TB_DT_F32 ? launch_gemv<__nv_bfloat16, float>(p, 1, s) : launch_gemv<__nv_bfloat16, __nv_bfloat16>(p, 1, s);
+  if (rc) return rc;
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

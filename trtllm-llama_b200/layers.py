@@ -112,8 +112,10 @@ class ClampedGatedMLP:
         self.dtype = w_down.dtype
 
     def forward(self, x, ctx):
-        gu = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
-        act = ops.gated_act(gu, self.dtype, self.alpha, self.limit, self.up_shift)
+        act = ops.linear_gated(x, self.w_gate_up, self.dtype, self.alpha, self.limit, self.up_shift)    # generation steps
+        if act is None:
+            gu = ops.linear(x, self.w_gate_up, out_dtype=torch.float32)
+            act = ops.gated_act(gu, self.dtype, self.alpha, self.limit, self.up_shift)
         return ops.linear(act, self.w_down, out_dtype=torch.float32)
 
 

@@ -57,7 +57,7 @@ def random_zobasun(torch, s, seed=0):
 class OpTimer:
     """Wraps the ragged operators of ``ops`` with CUDA-event timers and the bytes / flops each call moves."""
 
-    NAMES = ("linear", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
+    NAMES = ("linear", "linear_gated", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
              "latent_attention", "causal_conv1d", "rglru_scan")
 
     def __init__(self, torch, ops):
@@ -77,6 +77,11 @@ class OpTimer:
             kind = "fp32-fma" if kw.get("compute", 0) else ("batched" if B > 1 else "dense")
             return f"linear {kind} {a.shape[0]}x{N}x{K}" + (f"x{B}" if B > 1 else ""), 2.0 * a.shape[0] * N * K * B, \
                 nb(w) + a.shape[0] * B * K * a.element_size() + nb(o)
+        if name == "linear_gated":
+            if out is None:
+                return "linear_gated (not taken)", 0.0, 0
+            a, w = args[0], args[1]
+            return f"linear gated {a.shape[0]}x{w.shape[0]}x{w.shape[1]}", 2.0 * a.shape[0] * w.shape[0] * w.shape[1], nb(w, a, out)
         if name == "latent_attention":
             qa, pool, batch = args[0], args[1], args[2]
             heads, lat, rot = args[4], args[5], args[6]

@@ -445,6 +445,22 @@ def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=F
     return out
 
 
+def linear_gated(a, w_gate_up, out_dtype, alpha, limit, up_shift):
+    """gate‖up projection and the clamped gated activation in one kernel when the step has few rows (streaming GEMV);
+    returns None when the shape is not eligible — the caller then uses ``linear`` + ``gated_act``."""
+    _chk_dev(a, w_gate_up)
+    M, K, ff = a.shape[0], a.shape[1], w_gate_up.shape[0] // 2
+    if FORCE_TILE_LINEAR or M > 8 or w_gate_up.dtype != torch.bfloat16 or a.stride(1) != 1:
+        return None
+    out = torch.empty((M, ff), dtype=out_dtype, device=a.device)
+    rc = _rl.tb_linear_gated(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w_gate_up), _dt(w_gate_up),
+                             M, ff, K, float(alpha), float(limit), float(up_shift), _stream())
+    if rc == -3:
+        return None
+    check(rc, "tb_linear_gated")
+    return out
+
+
 def gated_act(gu, out_dtype, alpha, limit, up_shift):
     _chk_cuda(gu)
     rows, ff = gu.shape[0], gu.shape[1] // 2
