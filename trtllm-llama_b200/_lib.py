@@ -244,22 +244,38 @@ def build_library(target: str = "all"):
         raise LibraryNotBuilt(f"make {target} failed:\n{r.stdout[-4000:]}")
 
 
+def _up_to_date(target: str) -> bool:
+    """``make -q``: True when the target exists and no source is newer than it (False too when make cannot tell)."""
+    import subprocess
+    try:
+        return subprocess.run(["make", "-q", target], cwd=os.path.join(_HERE, "csrc"), stdout=subprocess.DEVNULL,
+                              stderr=subprocess.DEVNULL).returncode == 0
+    except OSError:
+        return False
+
+
 def load_ragged_library(build: bool = False):
     """The library that holds the ragged-batch operators: the full library when it is built (it contains them), else the
-    subset library, compiled on demand when ``build`` is set (a fresh checkout that only serves such a model)."""
+    subset library.  With ``build`` (the command-line tools pass it) a library whose sources changed since it was built is
+    not trusted: the full one is used only if ``make`` calls it up to date, and the subset is (re)compiled on demand — a
+    fresh checkout that only serves such a model compiles nine files and nothing else."""
     global _ragged
     if _ragged is not None:
         return _ragged
-    if os.path.exists(LIB_PATH):
+    if os.path.exists(LIB_PATH) and (not build or _up_to_date("all")):
         try:
             _ragged = load_library()
             return _ragged
         except (AttributeError, OSError):      # an older build without these operators: fall through to the subset
             pass
+    if build and not _up_to_date("ragged"):
+        try:
+            build_library("ragged")
+        except (LibraryNotBuilt, OSError):
+            if not os.path.exists(RAGGED_LIB_PATH):
+                raise
     if not os.path.exists(RAGGED_LIB_PATH):
-        if not build:
-            raise LibraryNotBuilt(f"{RAGGED_LIB_PATH} not found: run `make ragged` in csrc/ (there is no CPU fallback)")
-        build_library("ragged")
+        raise LibraryNotBuilt(f"{RAGGED_LIB_PATH} not found: run `make ragged` in csrc/ (there is no CPU fallback)")
     _ragged = _type(C.CDLL(RAGGED_LIB_PATH, mode=C.RTLD_GLOBAL), list(RAGGED_SIGNATURES) + list(_RAGGED_ALSO))
     return _ragged
 
