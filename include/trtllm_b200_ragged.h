@@ -24,7 +24,7 @@ extern "C" {
 #endif
 
 enum { TB_DT_F32 = 1, TB_DT_BF16 = 2 };
-enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1, TB_ACT_GATED = 2 /* tb_linear_gated only */ };
+enum { TB_ACT_NONE = 0, TB_ACT_GELU_TANH = 1, TB_ACT_GATED = 2 /* tb_linear_gated only */, TB_ACT_RELU_SQUARED = 3 /* max(z, 0)^2 */ };
 /* tb_linear compute paths: AUTO = tensor cores for bf16 weights, FMA for fp32 weights; FMA32 = fp32 multiply-add in a
  * fixed k order whatever the storage type (the all-32-bit mode, and the small products that feed a recurrence). */
 enum { TB_COMPUTE_AUTO = 0, TB_COMPUTE_FMA32 = 1, TB_COMPUTE_TILES = 2 /* bf16: the warp-MMA tiles at any row count (A/B) */ };
@@ -57,11 +57,20 @@ int tb_cast_rows_bf16(void* out, const float* x, int64_t ld, int rows, int cols,
 int tb_embed_scaled(float* out, const void* table, int t_dtype, const int* ids, float scale, int rows, int width,
                     int vocab, tb_stream_t stream);
 
-/* y = x / sqrt(mean(x^2) + eps) * (w + w_offset) over `cols` columns of each row; x fp32 with row stride ldi.
- * accumulate != 0: out (fp32) += y — the residual update of a layer that normalises the sublayer's OUTPUT;
- * else out = y in out_dtype.  w == NULL: no weight.  rows_idx != NULL: row r of out comes from row rows_idx[r] of x. */
+/* y = out_scale * x / sqrt(mean(x^2) + eps) * (w + w_offset) over `cols` columns of each row; x fp32 with row stride ldi.
+ * accumulate != 0: out (fp32) += y — the residual update of a layer that normalises the sublayer's OUTPUT (out_scale is
+ * then the layer's residual multiplier); else out = y in out_dtype.  w == NULL: no weight.  rows_idx != NULL: row r of out
+ * comes from row rows_idx[r] of x. */
 int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, int w_dtype,
-                    float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate, tb_stream_t stream);
+                    float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate, float out_scale,
+                    tb_stream_t stream);
+
+/* x[r, :cols] += vec (fp32 rows with stride ld; vec fp32 or bf16): the vector a pass of a looped block of layers adds to
+ * the residual stream. */
+int tb_add_row_vector(float* x, int64_t ld, const void* vec, int v_dtype, int rows, int cols, tb_stream_t stream);
+
+/* x <- cap * tanh(x / cap), in place over n fp32 values (soft cap of the logits). */
+int tb_tanh_cap(float* x, int64_t n, float cap, tb_stream_t stream);
 
 /* Gated feed-forward activation with clamps: g = min(gu[n, j], limit), u = clamp(gu[n, ff + j], -limit, limit),
  * out[n, j] = g * sigmoid(alpha * g) * (u + up_shift).  limit <= 0: no clamp.  gu fp32 [rows, 2 ff]. */
@@ -70,6 +79,11 @@ int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, fl
 
 /* cos / sin of pos * base^(-2 i / dims), i < dims / 2, for every row: table fp32 [N, dims / 2, 2] (angles in fp64). */
 int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream);
+/* The same with scaled frequencies (factor > 0): a frequency whose wavelength l = 2 pi / f exceeds original / low becomes
+ * f / factor, one with l < original / high stays, and between the two f' = (1 - s) f / factor + s f with
+ * s = (original / l - low) / (high - low). */
+int tb_rope_table_scaled(float* table, const int* tok_pos, int rows, int dims, double base, double factor, double low,
+                         double high, double original, tb_stream_t stream);
 
 /* Rotated tail of the queries into the attention operand: for head h of row n the `rot_dim` elements of q (fp32,
  * [N, H, dim + rot_dim]) behind the first `dim` are rotated pairwise (2i, 2i + 1) over their first `dims` elements by
@@ -105,8 +119,9 @@ int tb_latent_attention(void* out, const void* qa, const void* pool, int dtype, 
 int tb_causal_conv1d(float* out, const float* x, const void* w, const void* bias, int w_dtype, const float* state,
                      const int* tok_seq, const int* tok_pos, const int* seq_start, const int* seq_past,
                      const int* seq_slot, int rows, int channels, int taps, tb_stream_t stream);
-/* state[slot] <- the last taps - 1 inputs of (what it held ++ this step's rows); run after tb_causal_conv1d. */
-int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, const int* seq_len, const int* seq_past,
+/* state[slot] <- the last taps - 1 inputs of (what it held ++ this step's rows); run after the convolution.  x has row
+ * stride ldx (its first `channels` columns are the convolution's inputs). */
+int tb_causal_conv1d_update(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len, const int* seq_past,
                             const int* seq_slot, int seqs, int channels, int taps, tb_stream_t stream);
 
 /* Real-gated linear recurrent unit over a ragged batch.  gates fp32 [N, blocks, 2, C / blocks]: per block the
@@ -119,6 +134,59 @@ int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, 
 int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, const void* lam, int w_dtype, const void* y,
                   float* state, const int* seq_start, const int* seq_len, const int* seq_past, const int* seq_slot,
                   int seqs, int channels, int blocks, float c, int max_len, float* workspace, tb_stream_t stream);
+
+/* ---- windowed grouped-query attention with short convolutions, a softmax sink and output gates ------------------
+ * Pool entry of one position (type T): [kv_heads][dim] rotated keys, then [kv_heads][vdim] values.
+ *
+ * tb_qkv_conv_rope_append: proj fp32 [N, ldp] holds per row q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim)
+ * = C channels (further columns are ignored).  Each channel runs a causal convolution of `taps` taps (conv_w [C, taps],
+ * no bias; y_t = sum_j w[:, j] u_(t - taps + 1 + j)) over the row's portion and the carried inputs state[slot] (fp32
+ * [slots, taps - 1, C], oldest first; zeros before the sequence's start); then the first `dims` elements of every query
+ * and key head are rotated as interleaved pairs (2i, 2i + 1) by the row's table entry.  Queries go to q_out T [N, heads,
+ * dim]; keys and values to the row's position in its sequence's pages.  Carry the state on with
+ * tb_causal_conv1d_update(state, proj, ldp, ..., C, taps) afterwards. */
+int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* proj, int64_t ldp, const void* conv_w,
+                            int w_dtype, const float* state, const float* table, int dims, const int* tok_seq,
+                            const int* tok_pos, const int* seq_start, const int* seq_past, const int* seq_slot,
+                            const int* block_table, int max_blocks, int page, int rows, int heads, int kv_heads, int dim,
+                            int vdim, int taps, tb_stream_t stream);
+
+/* Attention of every row over the cached positions j of its sequence with 0 <= pos - j < window (window 0: all of
+ * 0..pos).  Query head h uses key/value head h / (heads / kv_heads).  score = scale * <q, k>; the softmax denominator
+ * also holds exp(sink[h]) (sink fp32 or bf16 [heads], or NULL for none): a term without key or value, not scaled.
+ * out T [N, heads, vdim] = softmax-weighted values, times sigmoid(gate[n, h]) when gate (fp32 logits, row stride ldg) is
+ * given.  Softmax in fp32; keys are visited in blocks of 32 absolute positions from the window's first block, so a row's
+ * result does not depend on how its prompt was cut or on the batch around it.  vdim <= 256.
+ * bf16 with 16 | dim, 16 | vdim, dim and vdim <= 256 runs on tensor cores (tb_window_attention_tensor_cores tells);
+ * mode 1 keeps any configuration on the SIMT kernel (A/B). */
+int tb_window_attention_tensor_cores(int dtype, int heads, int kv_heads, int dim, int vdim);
+int tb_window_attention(void* out, const void* q, const void* pool, int dtype, const float* gate, int64_t ldg,
+                        const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos, const int* block_table,
+                        int max_blocks, int page, int rows, int heads, int kv_heads, int dim, int vdim, float scale,
+                        int window, int mode, tb_stream_t stream);
+
+/* ---- routed-expert feed-forward ------------------------------------------------------------------------------------
+ * tb_moe_route: logits fp32 [N, experts].  s = sigmoid(logit); choice = s + correction (fp32 or bf16 [experts], NULL:
+ * none).  Experts form `groups` equal groups of neighbours; a group scores the sum of its two largest choices and only the
+ * `keep` best groups stay eligible.  The `top` largest eligible choices are taken (ties: lower index):
+ * ids int32 [N, top], weights fp32 [N, top] = s of the chosen experts (not renormalised). */
+int tb_moe_route(int* ids, float* weights, const float* logits, const void* correction, int c_dtype, int rows, int experts,
+                 int top, int groups, int keep, tb_stream_t stream);
+/* Plan: the N * top (token, choice) pairs sorted by expert, every expert's range padded to whole tiles of `tile` rows.
+ * tb_moe_plan_tiles = the number of tiles that is always enough; slot_pair int32 [max_tiles * tile] (pair index, -1 in
+ * the padding), tile_expert int32 [max_tiles] (-1: unused tile). */
+enum { TB_MOE_TILE = 64 };
+int tb_moe_plan_tiles(int pairs, int experts, int tile);
+int tb_moe_plan(int* slot_pair, int* tile_expert, const int* ids, int pairs, int experts, int tile, int max_tiles,
+                tb_stream_t stream);
+/* c = act(a w_e^T) tile by tile over the plan (tile height TB_MOE_TILE): w [experts, N, K].  a_div > 0: a [tokens, K] and
+ * slot s reads row slot_pair[s] / a_div; a_div == 0: a [slots, K].  c_by_pair != 0: C row = pair index, else the slot.
+ * compute as tb_linear (AUTO: tensor cores for bf16 weights). */
+int tb_moe_linear(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
+                  const int* slot_pair, const int* tile_expert, int max_tiles, int a_div, int c_by_pair, int N, int K, int act,
+                  int compute, tb_stream_t stream);
+/* out fp32 [N, width] = sum_k weights[n, k] * y[n * top + k, :]   (y fp32 [N * top, width], k in index order) */
+int tb_moe_combine(float* out, const float* y, const float* weights, int rows, int width, int top, tb_stream_t stream);
 
 #ifdef __cplusplus
 }

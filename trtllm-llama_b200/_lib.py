@@ -186,16 +186,29 @@ RAGGED_SIGNATURES = {
     "tb_gemm_tc_bf16": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, vp, sz, vp, vp]),
     "tb_cast_rows_bf16": (i32, [vp, vp, i64, i32, i32, vp]),
     "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),
-    "tb_rmsnorm_rows": (i32, [vp, i32, i64, vp, i64, vp, i32, f32, f32, vp, i32, i32, i32, vp]),
+    "tb_rmsnorm_rows": (i32, [vp, i32, i64, vp, i64, vp, i32, f32, f32, vp, i32, i32, i32, f32, vp]),
+    "tb_add_row_vector": (i32, [vp, i64, vp, i32, i32, i32, vp]),
+    "tb_tanh_cap": (i32, [vp, i64, f32, vp]),
     "tb_gated_act": (i32, [vp, i32, vp, i32, i32, f32, f32, f32, vp]),
     "tb_rope_table": (i32, [vp, vp, i32, i32, f64, vp]),
+    "tb_rope_table_scaled": (i32, [vp, vp, i32, i32, f64, f64, f64, f64, f64, vp]),
     "tb_rope_query_tail": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "tb_latent_kv_append": (i32, [vp, i32, vp, i64, vp, i32, f32, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
     "tb_latent_attention": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, vp]),
     "tb_latent_attention_tensor_cores": (i32, [i32, i32, i32]),
     "tb_causal_conv1d": (i32, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
-    "tb_causal_conv1d_update": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_causal_conv1d_update": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, vp]),
     "tb_rglru_scan": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp, vp]),
+    "tb_qkv_conv_rope_append": (i32, [vp, vp, i32, vp, i64, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                      i32, i32, i32, i32, vp]),
+    "tb_window_attention_tensor_cores": (i32, [i32, i32, i32, i32, i32]),
+    "tb_window_attention": (i32, [vp, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32,
+                                  i32, vp]),
+    "tb_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_moe_plan_tiles": (i32, [i32, i32, i32]),
+    "tb_moe_plan": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "tb_moe_linear": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "tb_moe_combine": (i32, [vp, vp, vp, i32, i32, i32, vp]),
 }
 SIGNATURES.update(RAGGED_SIGNATURES)
 # what libtrtllm_b200_ragged.so exports (csrc/Makefile target `ragged`): the operators above plus the sampling, arg-max
@@ -258,7 +271,7 @@ def load_ragged_library(build: bool = False):
     """The library that holds the ragged-batch operators: the full library when it is built (it contains them), else the
     subset library.  With ``build`` (the command-line tools pass it) a library whose sources changed since it was built is
     not trusted: the full one is used only if ``make`` calls it up to date, and the subset is (re)compiled on demand — a
-    fresh checkout that only serves such a model compiles nine files and nothing else."""
+    fresh checkout that only serves such a model compiles eleven files and nothing else."""
     global _ragged
     if _ragged is not None:
         return _ragged

@@ -40,7 +40,7 @@ struct GemmTcParams {
   int out_type;            // 0 fp16, 1 fp32, 2 int32, 3 bf16
   int bf16;                // KIND 0 only: operands are bf16 (same kind::f16 MMA, bf16 formats in the instruction descriptor)
   const void* bias;        // bf16 operands only: optional bf16 [N], added before the activation
-  int act;                 // bf16 operands only: 0 none, 1 tanh-GELU
+  int act;                 // bf16 operands only: 0 none, 1 tanh-GELU, 3 squared ReLU
   const __half* residual;  // optional [M, N] (fp16 out only)
   const __half* w_scale;   // KIND 2/3: [N] fp16
   const float* sc;         // KIND 1: per-channel [N] or [1]
@@ -220,6 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
         if (KIND == kGF16 && p.bf16) {
           v += bias_n;
           if (p.act == 1) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+          else if (p.act == 3) { v = fmaxf(v, 0.f); v *= v; }
           const size_t o = (size_t) m * p.N + n;
           if (p.out_type == 3) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
           else reinterpret_cast<float*>(p.c)[o] = v;
@@ -261,6 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
             for (int j = 0; j < 16; ++j) {
               f[j] = __uint_as_float(v[j]) + bias_n;
               if (p.act == 1) f[j] = 0.5f * f[j] * (1.f + tanhf(0.7978845608028654f * (f[j] + 0.044715f * f[j] * f[j] * f[j])));
+              else if (p.act == 3) { f[j] = fmaxf(f[j], 0.f); f[j] *= f[j]; }
             }
             if (p.out_type == 3) {
               __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(p.c) + (size_t) mc * p.N + n;
@@ -611,12 +613,12 @@ int tb_gemm_tc(int kind, void* c, int out_type, const void* x, const void* w, co
 }
 
 // bf16 operands through the same tcgen05 kernel (kind::f16 with bf16 formats): c = act(x w^T + bias), x [M, K] and w [N, K]
-// bf16 with K a multiple of 8, c [M, N] fp32 (out_type 1) or bf16 (3), bias bf16 [N] or NULL, act 0 | 1 (tanh-GELU).
+// bf16 with K a multiple of 8, c [M, N] fp32 (out_type 1) or bf16 (3), bias bf16 [N] or NULL, act 0 | 1 (tanh-GELU) | 3 (squared ReLU).
 // Used by the ragged-batch models for prompt-sized row counts; workspace / counters as tb_gemm_tc (split-K at <= 16 rows).
 extern "C" int tb_gemm_tc_bf16(void* c, int out_type, const void* x, const void* w, const void* bias, int act, int M, int N,
                                int K, void* workspace, size_t workspace_bytes, int* counters, cudaStream_t stream) {
   using namespace tb;
-  if (!c || !x || !w || M < 1 || N < 1 || K < 8 || K % 8 || (out_type != 1 && out_type != 3) || act < 0 || act > 1) return -1;
+  if (!c || !x || !w || M < 1 || N < 1 || K < 8 || K % 8 || (out_type != 1 && out_type != 3) || (act != 0 && act != 1 && act != 3)) return -1;
   if ((uintptr_t) x % 16 || (uintptr_t) w % 16) return -1;
   GemmTcParams p{};
   p.c = c; p.out_type = out_type; p.bf16 = 1; p.bias = bias; p.act = act;

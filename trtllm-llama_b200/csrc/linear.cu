@@ -34,12 +34,33 @@ __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == TB_ACT_GELU_TANH) return gelu_tanh(v);
+  if (act == TB_ACT_RELU_SQUARED) { v = fmaxf(v, 0.f); return v * v; }
+  return v;
+}
+
 struct LinArgs {
   void* c; const void* a; const void* w; const void* bias;
   int64_t ldc, c_bs, lda, a_bs, w_bs, bias_bs;
   int M, N, K, act;
   float alpha, limit, up_shift;      // TB_ACT_GATED (GEMV only): W holds N gate rows, then N up rows
+  // routed experts (tb_moe_linear): tile blockIdx.y belongs to expert tile_expert[blockIdx.y] (< 0: nothing to do) whose
+  // weights are batch element `expert` of W; tile row gm is slot gm of the plan, slot_pair[gm] its (token, choice) pair
+  // (< 0: padding).  A row = pair / a_div when a_div > 0 (the token's row), else the slot; C row = the pair when
+  // c_by_pair, else the slot.
+  const int* tile_expert; const int* slot_pair; int a_div, c_by_pair;
 };
+
+// row of A and of C behind tile row gm (-1: none)
+__device__ __forceinline__ void lin_rows(const LinArgs& p, int gm, int& ar, int& cr) {
+  if (gm >= p.M) { ar = cr = -1; return; }
+  if (!p.slot_pair) { ar = cr = gm; return; }
+  const int pair = p.slot_pair[gm];
+  if (pair < 0) { ar = cr = -1; return; }
+  ar = p.a_div > 0 ? pair / p.a_div : gm;
+  cr = p.c_by_pair ? pair : gm;
+}
 
 // ---------------------------------------------------------------------------------------------------------------
 template <typename AT, typename WT, typename CT>
@@ -47,12 +68,16 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
-  const int b = blockIdx.z;
+  __shared__ int a_rows[BM], c_rows[BM];
+  int b = blockIdx.z;
+  if (p.tile_expert) { b = p.tile_expert[blockIdx.y]; if (b < 0) return; }
   const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
   const WT* W = reinterpret_cast<const WT*>(p.w) + (int64_t) b * p.w_bs;
   CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;      // thread -> 4 rows (ty) x 4 cols (tx)
+  if (threadIdx.x < BM) lin_rows(p, m0 + threadIdx.x, a_rows[threadIdx.x], c_rows[threadIdx.x]);
+  __syncthreads();
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -62,8 +87,8 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
     // 64 x 16 elements per operand, 256 threads: 4 each; k fastest so global reads run along the rows
     for (int e = threadIdx.x; e < BM * BK; e += 256) {
       const int r = e / BK, k = e % BK;
-      const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
-      As[k][r] = (gm < p.M && gk < p.K) ? to_f<AT>(A[(int64_t) gm * p.lda + gk]) : 0.f;
+      const int gm = a_rows[r], gn = n0 + r, gk = k0 + k;
+      As[k][r] = (gm >= 0 && gk < p.K) ? to_f<AT>(A[(int64_t) gm * p.lda + gk]) : 0.f;
       Ws[k][r] = (gn < p.N && gk < p.K) ? to_f<WT>(W[(int64_t) gn * p.K + gk]) : 0.f;
     }
     __syncthreads();
@@ -84,15 +109,15 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
   const WT* bias = p.bias ? reinterpret_cast<const WT*>(p.bias) + (int64_t) b * p.bias_bs : nullptr;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int gm = m0 + ty * 4 + i;
-    if (gm >= p.M) continue;
+    const int gm = c_rows[ty * 4 + i];
+    if (gm < 0) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx * 4 + j;
       if (gn >= p.N) continue;
       float v = acc[i][j];
       if (bias) v += to_f<WT>(bias[gn]);
-      if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+      v = apply_act(v, p.act);
       C[(int64_t) gm * p.ldc + gn] = from_f<CT>(v);
     }
   }
@@ -110,7 +135,9 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
   constexpr int BM = 64, BN = 64, BK = 32, LD = BK + 8;       // 80-byte rows: fragment reads hit 32 distinct banks
   __shared__ __align__(16) __nv_bfloat16 As[BM][LD];
   __shared__ __align__(16) __nv_bfloat16 Ws[BN][LD];
-  const int b = blockIdx.z;
+  __shared__ int a_rows[BM], c_rows[BM];
+  int b = blockIdx.z;
+  if (p.tile_expert) { b = p.tile_expert[blockIdx.y]; if (b < 0) return; }
   const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
   const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) b * p.w_bs;
   CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
@@ -118,6 +145,8 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int wm = (warp / 2) * 32, wn = (warp % 2) * 32;
   const int g = lane / 4, t = lane % 4;
+  if (threadIdx.x < BM) lin_rows(p, m0 + threadIdx.x, a_rows[threadIdx.x], c_rows[threadIdx.x]);
+  __syncthreads();
   float acc[2][4][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i)
@@ -132,9 +161,9 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
     for (int it = 0; it < 2; ++it) {
       const int e = threadIdx.x + it * 128;
       const int r = e / 4, kc = (e % 4) * 8;
-      const int gm = m0 + r, gk = k0 + kc;
+      const int gm = a_rows[r], gk = k0 + kc;
       __align__(16) __nv_bfloat16 v[8];
-      if (gm < p.M && vec_a && gk + 8 <= p.K) {
+      if (gm >= 0 && vec_a && gk + 8 <= p.K) {
         const AT* src = A + (int64_t) gm * p.lda + gk;
         if constexpr (sizeof(AT) == 4) {
           const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
@@ -147,7 +176,7 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          v[j] = (gm < p.M && gk + j < p.K) ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) gm * p.lda + gk + j]))
+          v[j] = (gm >= 0 && gk + j < p.K) ? __float2bfloat16_rn(to_f<AT>(A[(int64_t) gm * p.lda + gk + j]))
                                             : __float2bfloat16_rn(0.f);
       }
       *reinterpret_cast<uint4*>(&As[r][kc]) = *reinterpret_cast<const uint4*>(v);
@@ -199,12 +228,12 @@ __global__ void __launch_bounds__(128) linear_mma_kernel(LinArgs p, int vec_a, i
     for (int j = 0; j < 4; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const int gm = m0 + wm + i * 16 + g + (k >= 2 ? 8 : 0);
+        const int gm = c_rows[wm + i * 16 + g + (k >= 2 ? 8 : 0)];
         const int gn = n0 + wn + j * 8 + 2 * t + (k & 1);
-        if (gm >= p.M || gn >= p.N) continue;
+        if (gm < 0 || gn >= p.N) continue;
         float v = acc[i][j][k];
         if (bias) v += __bfloat162float(bias[gn]);
-        if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+        v = apply_act(v, p.act);
         C[(int64_t) gm * p.ldc + gn] = from_f<CT>(v);
       }
 }
@@ -319,8 +348,7 @@ __global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p, int vec_a) 
 #pragma unroll
       for (int m = 0; m < MR; ++m) {
         if (m >= p.M) break;
-        float v = acc[m] + bv;
-        if (p.act == TB_ACT_GELU_TANH) v = gelu_tanh(v);
+        float v = apply_act(acc[m] + bv, p.act);
         C[(int64_t) m * p.ldc + n] = from_f<CT>(v);
       }
     }
@@ -375,7 +403,7 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
   if (M == 0) return 0;
   if (batch > 65535 || (M + 63) / 64 > 65535) return -2;
   if (act == TB_ACT_GATED) return -1;      // tb_linear_gated
-  LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act, 0.f, 0.f, 0.f};
+  LinArgs p{c, a, w, bias, ldc, c_bs, lda, a_bs, w_bs, bias_bs, M, N, K, act, 0.f, 0.f, 0.f, nullptr, nullptr, 0, 0};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 63) / 64, (M + 63) / 64, batch);
   if (compute == TB_COMPUTE_TILES && w_dtype != TB_DT_BF16) compute = TB_COMPUTE_AUTO;
@@ -424,6 +452,46 @@ extern "C" int tb_linear_gated(void* c, int c_dtype, int64_t ldc, const void* a,
   if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, 1, s) : launch_gemv<float, __nv_bfloat16>(p, 1, s);
   else rc = c_dtype == TB_DT_F32 ? launch_gemv<__nv_bfloat16, float>(p, 1, s) : launch_gemv<__nv_bfloat16, __nv_bfloat16>(p, 1, s);
   if (rc) return rc;
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Expert products over a plan (tb_moe_plan): the tile kernels above, tile row -> plan slot.  w [experts, N, K];
+// a_div > 0: A [tokens, K] and slot s reads row slot_pair[s] / a_div (the token of the pair); a_div == 0: A [slots, K].
+// c_by_pair: C row = the pair's index ([pairs, N]); else C row = the slot ([max_tiles * 64, N]).  Padding slots are neither
+// read nor written.  The tile height is 64 (TB_MOE_TILE).
+extern "C" int tb_moe_linear(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w,
+                             int w_dtype, const int* slot_pair, const int* tile_expert, int max_tiles, int a_div,
+                             int c_by_pair, int N, int K, int act, int compute, tb_stream_t stream) {
+  using namespace tb;
+  auto ok = [](int d) { return d == TB_DT_F32 || d == TB_DT_BF16; };
+  if (!c || !a || !w || !slot_pair || !tile_expert || !ok(c_dtype) || !ok(a_dtype) || !ok(w_dtype) || N <= 0 || K <= 0 ||
+      max_tiles < 0 || a_div < 0 || act == TB_ACT_GATED)
+    return -1;
+  if (max_tiles == 0) return 0;
+  if (max_tiles > 65535) return -2;
+  LinArgs p{c, a, w, nullptr, ldc, 0, lda, 0, (int64_t) N * K, 0, max_tiles * 64, N, K, act, 0.f, 0.f, 0.f,
+            tile_expert, slot_pair, a_div, c_by_pair};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((N + 63) / 64, max_tiles, 1);
+  if (w_dtype == TB_DT_BF16 && compute != TB_COMPUTE_FMA32) {
+    const int asz = a_dtype == TB_DT_F32 ? 4 : 2;
+    const int vec_a = ((uintptr_t) a % 16 == 0) && (lda * asz % 16 == 0);
+    const int vec_w = ((uintptr_t) w % 16 == 0) && (K % 8 == 0);
+    if (a_dtype == TB_DT_F32) {
+      if (c_dtype == TB_DT_F32) linear_mma_kernel<float, float><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+      else linear_mma_kernel<float, __nv_bfloat16><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+    } else {
+      if (c_dtype == TB_DT_F32) linear_mma_kernel<__nv_bfloat16, float><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+      else linear_mma_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
+    }
+  } else if (w_dtype == TB_DT_BF16) {
+    if (a_dtype == TB_DT_F32) launch_fma<float, __nv_bfloat16>(p, c_dtype, grid, s);
+    else launch_fma<__nv_bfloat16, __nv_bfloat16>(p, c_dtype, grid, s);
+  } else {
+    if (a_dtype == TB_DT_F32) launch_fma<float, float>(p, c_dtype, grid, s);
+    else launch_fma<__nv_bfloat16, float>(p, c_dtype, grid, s);
+  }
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,195 @@
+// Routed-expert feed-forward over a ragged batch: the router's choice, the plan that sorts (token, choice) pairs by
+// expert, and the weighted sum of the chosen experts' outputs.  The expert products themselves are tb_moe_linear
+// (linear.cu): the tile kernels of tb_linear walking the plan.
+//
+//   moe_route_kernel    one warp per token: s = sigmoid(logit); choice = s + correction; experts form `groups` equal
+//                       groups of neighbours, a group scores the sum of its two largest choices, only the `keep` best
+//                       groups stay eligible; the `top` largest eligible choices are taken (ties: the lower index), and
+//                       their weights are the plain s, not renormalised.  All fp32.
+//   moe_plan_kernel     one CTA: pairs counted per expert, every expert's range padded to whole tiles of `tile` rows
+//                       (so a tile never mixes experts), tile -> expert table, and sorted slot -> pair index (-1 in the
+//                       padding).  Everything stays on the device: a replayed step graph re-plans with the same launch.
+//   moe_combine_kernel  out[n] = sum_k weight[n, k] * y[n * top + k], k in index order.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "../../include/trtllm_b200_ragged.h"
+
+namespace tb {
+namespace {
+
+__device__ __forceinline__ float ld_w(const void* p, int dtype, int64_t i) {
+  return dtype == TB_DT_F32 ? reinterpret_cast<const float*>(p)[i]
+                            : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+// arg-max over the warp's (value, index) candidates; ties go to the lower index; index -1 = no candidate
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (oi >= 0 && (i < 0 || ov > v || (ov == v && oi < i))) { v = ov; i = oi; }
+  }
+}
+
+constexpr int kRouteWarps = 4;
+
+// shared memory per warp: choice [E] | sigmoid [E] | state [E] (0 eligible, 1 masked, 2 taken) | group score [groups]
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(int* ids, float* weights, const float* logits,
+                                                                     const void* corr, int c_dtype, int rows, int E, int top,
+                                                                     int groups, int keep) {
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int row = blockIdx.x * kRouteWarps + warp;
+  if (row >= rows) return;
+  float* choice = smem + (size_t) warp * (3 * E + groups);
+  float* sig = choice + E;
+  int* state = reinterpret_cast<int*>(sig + E);
+  float* gscore = reinterpret_cast<float*>(state + E);
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.f / (1.f + expf(-logits[(int64_t) row * E + e]));
+    sig[e] = s;
+    choice[e] = s + (corr ? ld_w(corr, c_dtype, e) : 0.f);
+    state[e] = 0;
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;              // the two largest of the group
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float c = choice[e];
+        if (c > a) { b = a; a = c; } else if (c > b) b = c;
+      }
+      gscore[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // mark everything masked, then free the `keep` best groups
+    for (int e = lane; e < E; e += 32) state[e] = 1;
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float bv = -INFINITY; int bi = -1;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gscore[g];
+        if (v == v && state[g * per] == 1 && (bi < 0 || v > bv)) { bv = v; bi = g; }
+      }
+      warp_argmax(bv, bi);
+      if (bi < 0) break;
+      for (int e = bi * per + lane; e < (bi + 1) * per; e += 32) state[e] = 0;
+      __syncwarp();
+    }
+  }
+  for (int k = 0; k < top; ++k) {
+    float bv = -INFINITY; int bi = -1;
+    for (int e = lane; e < E; e += 32)
+      if (state[e] == 0 && (bi < 0 || choice[e] > bv)) { bv = choice[e]; bi = e; }
+    warp_argmax(bv, bi);
+    if (bi < 0) {                                        // fewer eligible experts than `top`: fall back to masked ones
+      for (int e = lane; e < E; e += 32)
+        if (state[e] == 1 && (bi < 0 || choice[e] > bv)) { bv = choice[e]; bi = e; }
+      warp_argmax(bv, bi);
+    }
+    if (lane == 0) {
+      ids[(int64_t) row * top + k] = bi < 0 ? 0 : bi;
+      weights[(int64_t) row * top + k] = bi < 0 ? 0.f : sig[bi];
+      if (bi >= 0) state[bi] = 2;
+    }
+    __syncwarp();
+  }
+}
+
+// one CTA of 1024 threads; shared: count [E] | cursor [E]
+__global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* tile_expert, const int* ids, int pairs, int E,
+                                                        int tile, int max_tiles) {
+  extern __shared__ int sm_i[];
+  int* count = sm_i;
+  int* cursor = sm_i + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_expert[t] = -1;
+  for (int s = threadIdx.x; s < max_tiles * tile; s += blockDim.x) slot_pair[s] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+    for (int e = 0; e < E; ++e) {
+      const int nt = (count[e] + tile - 1) / tile;
+      cursor[e] = t * tile;
+      for (int k = 0; k < nt && t + k < max_tiles; ++k) tile_expert[t + k] = e;
+      t += nt;
+    }
+  }
+  __syncthreads();
+  // a pair's slot inside its expert's range is whatever the atomic hands out: every output row is computed from its own
+  // input row alone, in a k order of its own, so the slot does not reach the result
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < E) {
+      const int s = atomicAdd(&cursor[e], 1);
+      if (s < max_tiles * tile) slot_pair[s] = p;
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(float* out, const float* y, const float* weights, int64_t n, int width, int top) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+    const int64_t row = i / width;
+    const int c = (int) (i % width);
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(weights[row * top + k], y[(row * top + k) * width + c], acc);
+    out[i] = acc;
+  }
+}
+
+}  // namespace
+}  // namespace tb
+
+using namespace tb;
+
+extern "C" int tb_moe_route(int* ids, float* weights, const float* logits, const void* correction, int c_dtype, int rows,
+                            int experts, int top, int groups, int keep, tb_stream_t stream) {
+  if (!ids || !weights || !logits || rows < 0 || experts <= 0 || top <= 0 || top > experts || groups <= 0 ||
+      experts % groups || keep <= 0 || keep > groups)
+    return -1;
+  if (correction && c_dtype != TB_DT_F32 && c_dtype != TB_DT_BF16) return -1;
+  const size_t smem = (size_t) kRouteWarps * (3 * experts + groups) * sizeof(float);
+  if (smem > 48 * 1024) return -2;
+  if (rows == 0) return 0;
+  moe_route_kernel<<<(rows + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, (cudaStream_t) stream>>>(
+      ids, weights, logits, correction, c_dtype, rows, experts, top, groups, keep);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_moe_plan_tiles(int pairs, int experts, int tile) {
+  if (pairs < 0 || experts <= 0 || tile <= 0) return -1;
+  const int full = (pairs + tile - 1) / tile;
+  return full + (experts < pairs ? experts : pairs);      // every expert in use may end in one partly filled tile
+}
+
+extern "C" int tb_moe_plan(int* slot_pair, int* tile_expert, const int* ids, int pairs, int experts, int tile, int max_tiles,
+                           tb_stream_t stream) {
+  if (!slot_pair || !tile_expert || !ids || pairs < 0 || experts <= 0 || tile <= 0 || max_tiles < tb_moe_plan_tiles(pairs, experts, tile))
+    return -1;
+  if ((size_t) experts * 2 * sizeof(int) > 48 * 1024) return -2;
+  if (pairs == 0) return 0;
+  moe_plan_kernel<<<1, 1024, (size_t) experts * 2 * sizeof(int), (cudaStream_t) stream>>>(slot_pair, tile_expert, ids, pairs,
+                                                                                         experts, tile, max_tiles);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_moe_combine(float* out, const float* y, const float* weights, int rows, int width, int top,
+                              tb_stream_t stream) {
+  if (!out || !y || !weights || rows < 0 || width <= 0 || top <= 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * width;
+  const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, y, weights, n, width, top);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}

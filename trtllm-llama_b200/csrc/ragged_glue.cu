@@ -30,7 +30,7 @@ __global__ void embed_scaled_kernel(float* out, const void* table, int t_dtype, 
 // one CTA per row; the sum of squares is reduced in a fixed tree (warp shuffles, then warp 0 over the warp sums)
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi,
                                                            const void* w, int w_dtype, float w_offset, float eps,
-                                                           const int* rows_idx, int cols, int accumulate) {
+                                                           const int* rows_idx, int cols, int accumulate, float out_scale) {
   __shared__ float red[8];
   __shared__ float inv_s;
   const int row = blockIdx.x;
@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(void* out, int out_dt
   for (int c = threadIdx.x; c < cols; c += 256) {
     float y = xr[c] * inv;
     if (w) y *= ld_f(w, w_dtype, c) + w_offset;
+    y *= out_scale;
     const int64_t o = (int64_t) row * ldo + c;
     if (accumulate) reinterpret_cast<float*>(out)[o] += y;
     else st_f(out, out_dtype, o, y);
@@ -74,15 +75,39 @@ __global__ void cast_rows_bf16_kernel(__nv_bfloat16* out, const float* x, int64_
     out[i] = __float2bfloat16_rn(x[(i / cols) * ld + i % cols]);
 }
 
-__global__ void rope_table_kernel(float* table, const int* tok_pos, int rows, int half, int dims, double base) {
+// factor > 0: wavelengths above original / low turn `factor` times slower, those below original / high are kept, and the
+// band between is blended linearly in original / wavelength
+__global__ void rope_table_kernel(float* table, const int* tok_pos, int rows, int half, int dims, double base, double factor,
+                                  double low, double high, double original) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * half) return;
   const int row = i / half, f = i % half;
-  const double freq = pow(base, -2.0 * (double) f / (double) dims);
+  double freq = pow(base, -2.0 * (double) f / (double) dims);
+  if (factor > 0.0) {
+    const double wavelength = 6.283185307179586476925 / freq;
+    if (wavelength > original / low) {
+      freq /= factor;
+    } else if (!(wavelength < original / high)) {
+      const double s = (original / wavelength - low) / (high - low);
+      freq = (1.0 - s) * freq / factor + s * freq;
+    }
+  }
   double s, c;
   sincos((double) tok_pos[row] * freq, &s, &c);
   table[2 * (int64_t) i] = (float) c;
   table[2 * (int64_t) i + 1] = (float) s;
+}
+
+// x[r, :] += vec — the vector a pass of a looped block adds to the residual stream before its first layer
+__global__ void add_row_vector_kernel(float* x, int64_t ld, const void* vec, int v_dtype, int cols, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x)
+    x[(i / cols) * ld + i % cols] += ld_f(vec, v_dtype, i % cols);
+}
+
+// x <- cap * tanh(x / cap): soft cap of the logits
+__global__ void tanh_cap_kernel(float* x, int64_t n, float cap) {
+  for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
 }
 
 __global__ void rope_query_tail_kernel(void* qa, int dtype, const float* q, const float* table, int rows, int heads, int dim,
@@ -124,12 +149,12 @@ extern "C" int tb_embed_scaled(float* out, const void* table, int t_dtype, const
 
 extern "C" int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64_t ldi, const void* w, int w_dtype,
                                float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate,
-                               tb_stream_t stream) {
+                               float out_scale, tb_stream_t stream) {
   if (!out || !x || !dt_ok(out_dtype) || (w && !dt_ok(w_dtype)) || cols <= 0 || rows < 0) return -1;
   if (accumulate && out_dtype != TB_DT_F32) return -2;
   if (rows == 0) return 0;
   rmsnorm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, ldo, x, ldi, w, w_dtype, w_offset, eps,
-                                                               rows_idx, cols, accumulate);
+                                                               rows_idx, cols, accumulate, out_scale);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -155,11 +180,37 @@ extern "C" int tb_cast_rows_bf16(void* out, const float* x, int64_t ld, int rows
   return 0;
 }
 
-extern "C" int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream) {
+extern "C" int tb_rope_table_scaled(float* table, const int* tok_pos, int rows, int dims, double base, double factor,
+                                    double low, double high, double original, tb_stream_t stream) {
   if (!table || !tok_pos || dims <= 0 || dims % 2 || rows < 0 || !(base > 0.0)) return -1;
+  if (factor > 0.0 && (!(low > 0.0) || !(high > low) || !(original > 0.0))) return -1;
   if (rows == 0) return 0;
   const int n = rows * (dims / 2);
-  rope_table_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(table, tok_pos, rows, dims / 2, dims, base);
+  rope_table_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(table, tok_pos, rows, dims / 2, dims, base, factor,
+                                                                        low, high, original);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream) {
+  return tb_rope_table_scaled(table, tok_pos, rows, dims, base, 0.0, 0.0, 0.0, 0.0, stream);
+}
+
+extern "C" int tb_add_row_vector(float* x, int64_t ld, const void* vec, int v_dtype, int rows, int cols, tb_stream_t stream) {
+  if (!x || !vec || !dt_ok(v_dtype) || cols <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  const int64_t n = (int64_t) rows * cols;
+  const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  add_row_vector_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(x, ld, vec, v_dtype, cols, n);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_tanh_cap(float* x, int64_t n, float cap, tb_stream_t stream) {
+  if (!x || n < 0 || !(cap > 0.f)) return -1;
+  if (n == 0) return 0;
+  const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  tanh_cap_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(x, n, cap);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

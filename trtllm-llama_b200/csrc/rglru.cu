@@ -41,7 +41,7 @@ __global__ void causal_conv1d_kernel(float* out, const float* x, const void* w, 
 }
 
 // one thread per (sequence, channel): reads every old value it needs before it writes
-__global__ void causal_conv1d_update_kernel(float* state, const float* x, const int* seq_start, const int* seq_len,
+__global__ void causal_conv1d_update_kernel(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len,
                                             const int* seq_past, const int* seq_slot, int seqs, int channels, int taps) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= seqs * channels) return;
@@ -53,7 +53,7 @@ __global__ void causal_conv1d_update_kernel(float* state, const float* x, const 
   for (int j = 0; j < n; ++j) {
     const int p = past + len - n + j;                // absolute position the new state row j holds
     float v = 0.f;
-    if (p >= past) v = x[(int64_t) (start + (p - past)) * channels + ch];
+    if (p >= past) v = x[(int64_t) (start + (p - past)) * ldx + ch];
     else if (p >= 0) v = st[(int64_t) (n - (past - p)) * channels + ch];
     keep[j] = v;
   }
@@ -177,7 +177,7 @@ extern "C" int tb_causal_conv1d(float* out, const float* x, const void* w, const
   return 0;
 }
 
-extern "C" int tb_causal_conv1d_update(float* state, const float* x, const int* seq_start, const int* seq_len,
+extern "C" int tb_causal_conv1d_update(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len,
                                        const int* seq_past, const int* seq_slot, int seqs, int channels, int taps,
                                        tb_stream_t stream) {
   if (!state || !x || !seq_start || !seq_len || !seq_past || !seq_slot || channels <= 0 || taps < 1 || taps > kMaxTaps ||
@@ -185,7 +185,7 @@ extern "C" int tb_causal_conv1d_update(float* state, const float* x, const int* 
     return -1;
   if (seqs == 0 || taps == 1) return 0;
   const int n = seqs * channels;
-  causal_conv1d_update_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(state, x, seq_start, seq_len, seq_past,
+  causal_conv1d_update_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(state, x, ldx, seq_start, seq_len, seq_past,
                                                                                    seq_slot, seqs, channels, taps);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;

@@ -3,10 +3,10 @@
 One ``InflightSession.step`` runs an arbitrary mix of sequences — a portion of one prompt of any length beside single
 generated tokens of others — as one ragged batch over the model's kernels.  Between steps a sequence lives in
 
-  * pages of the latent-cache pools (one pool per caching layer, the same block ids in every layer), dealt by
-    ``runtime.KVCacheManager`` (``reserve`` / ``release``), and
-  * one slot of the recurrent-state buffers (per recurrent layer: the recurrence state and the convolution's carried
-    inputs), dealt by ``StateSlotManager``.
+  * pages of the cache pools (one pool per caching layer and pass of a looped block — latent entries or keys and values —
+    the same block ids in every pool), dealt by ``runtime.KVCacheManager`` (``reserve`` / ``release``), and
+  * one slot of the state buffers (per layer that has them: the recurrence state and / or the carried inputs of its short
+    convolutions), dealt by ``StateSlotManager``.
 
 ``InflightScheduler`` + ``InflightSession.generate`` are the generation entry point: admission by free slots and pages,
 chunked prefill under a per-step token budget beside the running decodes, sampling with the library's sampling kernels
@@ -98,10 +98,11 @@ class StepContext:
         self.batch, self.pools, self.states, self.page = batch, pools, states, page
         self._tables = {}
 
-    def rope_table(self, dims, base):
-        key = (int(dims), float(base))
+    def rope_table(self, dims, base, scaling=None):
+        """One table per (dims, base, frequency scaling) and step, shared by every layer that rotates that way."""
+        key = (int(dims), float(base), tuple(scaling) if scaling else None)
         if key not in self._tables:
-            self._tables[key] = ops.rope_table(self.batch.tok_pos, dims, base)
+            self._tables[key] = ops.rope_table(self.batch.tok_pos, dims, base, scaling)
         return self._tables[key]
 
 
@@ -124,11 +125,12 @@ class InflightSession:
         blocks = max(1, -(-int(max_tokens) // self.page))
         self.kv_cache_manager = KVCacheManager(blocks=blocks, tokens_per_block=self.page, max_blocks_per_seq=blocks)
         self.slot_manager = StateSlotManager(max_seqs)
-        self.pools = {i: torch.empty((blocks * self.page, width), dtype=model.dtype, device=self.device)
-                      for i, width in model.cache_layers().items()}
-        self.states = {i: (torch.zeros((max_seqs, max(taps - 1, 1), ch), dtype=torch.float32, device=self.device),
-                           torch.zeros((max_seqs, ch), dtype=torch.float32, device=self.device))
-                       for i, (taps, ch) in model.state_layers().items()}
+        # keyed by (layer, pass): a layer that a looped block runs several times holds one pool / state per pass
+        self.pools = {k: torch.empty((blocks * self.page, width), dtype=model.dtype, device=self.device)
+                      for k, width in model.cache_layers().items()}
+        self.states = {k: (torch.zeros((max_seqs, max(taps - 1, 1), ch), dtype=torch.float32, device=self.device),
+                           torch.zeros((max_seqs, ch), dtype=torch.float32, device=self.device) if recurrent else None)
+                       for k, (taps, ch, recurrent) in model.state_layers().items()}
         self.live = {}
         self._next_idx = 0
 

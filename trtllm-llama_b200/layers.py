@@ -49,7 +49,13 @@ class LatentAttention:
     def cache_entry(self):
         return self.lat + self.rot_dim
 
-    def forward(self, x, ctx):
+    def cache_entries(self):
+        return {"own": self.cache_entry} if self.owns_cache else {}
+
+    def conv_state(self):
+        return None
+
+    def forward(self, x, ctx, rep=0):
         n, H, dn, dr, R = x.shape[0], self.heads, self.dim, self.rot_dim, self.lat
         f32 = torch.float32
         cq = ops.rmsnorm_rows(ops.linear(x, self.w_dq, out_dtype=f32), self.w_dq_norm, self.eps, out_dtype=self.dtype)
@@ -57,12 +63,12 @@ class LatentAttention:
         table = ctx.rope_table(self.rot_dims, self.rot_base)
         if self.owns_cache:
             kv = ops.linear(x, self.w_dkv, out_dtype=f32)
-            ops.latent_kv_append(ctx.pools[self.index], kv, self.w_dkv_norm, self.eps, table, self.rot_dims, ctx.batch,
+            ops.latent_kv_append(ctx.pools[(self.index, rep)], kv, self.w_dkv_norm, self.eps, table, self.rot_dims, ctx.batch,
                                  ctx.page, R, dr)
         qa = torch.empty((n, H, R + dr), dtype=self.dtype, device=x.device)
         ops.linear(q.view(n, H, dn + dr)[:, :, :dn], self.w_uk_t, out=qa[:, :, :R])
         ops.rope_query_tail(qa, q, table, H, dn, dr, self.rot_dims, R)
-        lat_out = ops.latent_attention(qa, ctx.pools[self.kv_source], ctx.batch, ctx.page, H, R, dr, self.scale)
+        lat_out = ops.latent_attention(qa, ctx.pools[(self.kv_source, rep)], ctx.batch, ctx.page, H, R, dr, self.scale)
         heads_out = torch.empty((n, H, self.vdim), dtype=self.dtype, device=x.device)
         ops.linear(lat_out, self.w_uv, out=heads_out)
         return ops.linear(heads_out.view(n, H * self.vdim), self.w_o, out_dtype=f32)
@@ -89,17 +95,112 @@ class GatedLinearRecurrence:
         self.b_gates = torch.cat([b_ra, b_ri], dim=1).contiguous()       # [blocks, 2 bw]
         self.lam, self.w_o = lam, w_o
 
-    def forward(self, x, ctx):
+    def cache_entries(self):
+        return {}
+
+    def conv_state(self):
+        return (self.taps, self.channels, True)
+
+    def forward(self, x, ctx, rep=0):
         n, f32 = x.shape[0], torch.float32
         bw = self.channels // self.blocks
         y = ops.linear(x, self.w_y, bias=self.b_y, out_dtype=self.dtype, act=ops.ACT_GELU_TANH)
         xb = ops.linear(x, self.w_x, bias=self.b_x, out_dtype=f32)
-        conv_state, rec_state = ctx.states[self.index]
+        conv_state, rec_state = ctx.states[(self.index, rep)]
         u = ops.causal_conv1d(xb, self.conv_w, self.conv_b, conv_state, ctx.batch)
         gates = torch.empty((n, self.blocks, 2 * bw), dtype=f32, device=x.device)
         ops.linear(u.view(n, self.blocks, bw), self.w_gates, bias=self.b_gates, out=gates, compute=ops.COMPUTE_FMA32)
         s = ops.rglru_scan(u, gates, self.lam, y, rec_state, ctx.batch, self.blocks, self.decay_scale)
         return ops.linear(s, self.w_o, out_dtype=f32)
+
+
+class WindowedAttention:
+    """Grouped-query attention over a sliding window with short convolutions, a softmax sink and per-head output gates.
+
+    q = W_q h, k = W_k h, v = W_v h (``heads`` query heads and ``kv_heads`` key/value heads of size ``dim``; values of
+    size ``vdim``; query head i reads key/value head i // (heads / kv_heads)).  Every channel of q, k and v then runs a
+    causal convolution over time with ``taps`` taps (y_t = sum_j c[:, j] u_(t - taps + 1 + j)), and the first
+    ``rot_dims`` elements of each query and key head are rotated as interleaved pairs (2i, 2i + 1) by position times
+    base^(-2i / rot_dims), optionally with the long wavelengths slowed (``rot_scaling`` = (factor, low, high, original)).
+    score(i, j) = scale * q_i . k_j for 0 <= i - j < window (window 0: all j <= i); the softmax denominator holds one
+    more term exp(sink_head) without a value; head outputs are multiplied by sigmoid(W_g h)_head and projected by W_o.
+
+    The four input projections are ONE product against the stacked [q | k | v | g] rows.  Per sequence the layer carries
+    the last taps - 1 projected q | k | v rows (fp32) in a state slot and its rotated keys and values in pages of a pool
+    (entry = [kv_heads * dim keys | kv_heads * vdim values])."""
+
+    def __init__(self, index, *, heads, kv_heads, dim, vdim, taps, scale, window=0, rot_dims=0, rot_base=10000.0,
+                 rot_scaling=None, w_q, w_k, w_v, conv_q, conv_k, conv_v, w_o, sink=None, w_g=None):
+        if heads % kv_heads:
+            raise ValueError(f"layer {index}: {heads} query heads do not split over {kv_heads} key/value heads")
+        if rot_dims % 2 or rot_dims > dim or (rot_dims and dim % 2):
+            raise ValueError(f"layer {index}: rotary dims {rot_dims} must be even and at most the (even) head size {dim}")
+        self.index, self.heads, self.kv_heads, self.dim, self.vdim, self.taps = index, heads, kv_heads, dim, vdim, int(taps)
+        self.scale, self.window, self.rot_dims, self.rot_base = float(scale), int(window or 0), int(rot_dims), float(rot_base)
+        self.rot_scaling = tuple(float(v) for v in rot_scaling) if rot_scaling else None
+        self.dtype = w_q.dtype
+        self.channels = heads * dim + kv_heads * (dim + vdim)
+        self.w_in = torch.cat([w_q, w_k, w_v] + ([w_g] if w_g is not None else []), dim=0).contiguous()
+        self.conv_w = torch.cat([conv_q, conv_k, conv_v], dim=0).contiguous()
+        if self.conv_w.shape != (self.channels, self.taps):
+            raise ValueError(f"layer {index}: convolution weights {tuple(self.conv_w.shape)} != {(self.channels, self.taps)}")
+        self.gated, self.sink, self.w_o = w_g is not None, sink, w_o
+
+    def cache_entries(self):
+        return {"own": self.kv_heads * (self.dim + self.vdim)}
+
+    def conv_state(self):
+        return (self.taps, self.channels, False)
+
+    def forward(self, x, ctx, rep=0):
+        n, key = x.shape[0], (self.index, rep)
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        table = ctx.rope_table(self.rot_dims, self.rot_base, self.rot_scaling) if self.rot_dims else None
+        q = ops.qkv_conv_rope_append(proj, self.conv_w, ctx.states[key][0], table, self.rot_dims, ctx.pools[key], ctx.batch,
+                                     ctx.page, self.heads, self.kv_heads, self.dim, self.vdim)
+        o = ops.window_attention(q, ctx.pools[key], ctx.batch, ctx.page, self.kv_heads, self.vdim, self.scale, self.window,
+                                 sink=self.sink, gate=proj[:, self.channels:] if self.gated else None)
+        return ops.linear(o.view(n, self.heads * self.vdim), self.w_o, out_dtype=torch.float32)
+
+
+class SquaredReluMLP:
+    """out = W_down max(W_up h, 0)^2; the activation is the up projection's epilogue."""
+
+    def __init__(self, *, w_up, w_down):
+        self.w_up, self.w_down, self.dtype = w_up, w_down, w_down.dtype
+
+    def forward(self, x, ctx):
+        return ops.linear(ops.linear(x, self.w_up, out_dtype=self.dtype, act=ops.ACT_RELU_SQUARED), self.w_down,
+                          out_dtype=torch.float32)
+
+
+class RoutedExpertsMLP:
+    """Mixture of gated experts: each token runs ``top`` of ``experts`` small feed-forwards W_down (silu(W_gate h) * W_up h).
+
+    Router (fp32): s = sigmoid(W_router h); choice = s + correction; the experts form ``groups`` equal groups of
+    neighbours, a group scores the sum of its two largest choices and only the ``keep`` best groups stay eligible; the
+    ``top`` largest eligible choices are taken and weighted by their plain s (not renormalised).  The (token, choice)
+    pairs are sorted by expert on the device into whole tiles and both expert products walk that plan, so a step costs
+    ``top`` experts per token whatever the batch."""
+
+    def __init__(self, *, w_router, correction, w_gate, w_up, w_down, top, groups=1, keep=1):
+        """w_gate, w_up: [experts, ff, width]; w_down: [experts, width, ff]."""
+        self.experts, self.top, self.groups, self.keep = w_gate.shape[0], int(top), int(groups), int(keep)
+        if self.experts % self.groups or not 1 <= self.keep <= self.groups or not 1 <= self.top <= self.experts:
+            raise ValueError(f"router: {self.experts} experts, {groups} groups (keep {keep}), top {top}")
+        self.w_router, self.correction = w_router, correction
+        self.w_gate_up = torch.cat([w_gate, w_up], dim=1).contiguous()      # [experts, 2 ff, width]: gate rows, then up rows
+        self.w_down, self.dtype = w_down.contiguous(), w_down.dtype
+
+    def forward(self, x, ctx):
+        n = x.shape[0]
+        logits = ops.linear(x, self.w_router, out_dtype=torch.float32, compute=ops.COMPUTE_FMA32)
+        ids, weights = ops.moe_route(logits, self.correction, self.top, self.groups, self.keep)
+        slot_pair, tile_expert = ops.moe_plan(ids, self.experts)
+        gu = ops.moe_linear(x, self.w_gate_up, slot_pair, tile_expert, a_div=self.top, c_rows=0, out_dtype=torch.float32)
+        act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)                  # silu(gate) * up
+        y = ops.moe_linear(act, self.w_down, slot_pair, tile_expert, a_div=0, c_rows=n * self.top, out_dtype=torch.float32)
+        return ops.moe_combine(y, weights)
 
 
 class ClampedGatedMLP:
@@ -122,32 +223,68 @@ class ClampedGatedMLP:
 class LayerStackModel:
     """Embedding, a stack of (mixer, optional feed-forward) layers, output norm and head.
 
-    ``post_norm`` stacks normalise each sublayer's OUTPUT and add it to the residual, x <- x + norm(f(x)), with
-    norm weights stored around zero (``norm_offset`` = 1); the sublayers read the residual itself."""
+    A layer is a dict: ``mixer``, ``mlp`` (or None) and per sublayer a norm weight applied to its INPUT (``pre1`` /
+    ``pre2``, None: the sublayer reads the residual stream itself) and one applied to its OUTPUT (``post1`` / ``post2``):
+    x <- x + residual_mult * norm_post(f(norm_pre(x))).  Norm weights are stored around ``norm_offset`` below 1 (the
+    multiplier is w + norm_offset).
 
-    def __init__(self, *, vocab, width, dtype, embed, embed_scale, layers, final_norm, head, eps, norm_offset=1.0):
+    ``loop`` = (start, stop, times): layers start .. stop - 1 run ``times`` times in a row with the same weights; every
+    pass has caches and states of its own, and row t of ``loop_step`` is added to the residual stream right before pass
+    t's first layer.  ``logit_cap`` > 0: logits <- cap * tanh(logits / cap)."""
+
+    def __init__(self, *, vocab, width, dtype, embed, layers, final_norm, head, eps, embed_scale=1.0, norm_offset=0.0,
+                 residual_mult=1.0, loop=None, loop_step=None, logit_cap=0.0):
         self.vocab, self.width, self.dtype, self.eps, self.norm_offset = vocab, width, dtype, float(eps), float(norm_offset)
         self.embed, self.embed_scale, self.layers, self.final_norm, self.head = embed, float(embed_scale), layers, final_norm, head
+        self.residual_mult, self.logit_cap, self.loop_step = float(residual_mult), float(logit_cap or 0.0), loop_step
+        for l in layers:
+            for k in ("pre1", "post1", "pre2", "post2"):
+                l.setdefault(k, None)
+        n = len(layers)
+        if loop is None or loop[1] <= loop[0]:
+            self.runs = [(i, 0, False) for i in range(n)]
+        else:
+            start, stop, times = (int(v) for v in loop)
+            if not (0 <= start < stop <= n) or times < 1:
+                raise ValueError(f"loop {loop} does not fit {n} layers")
+            if loop_step is not None and tuple(loop_step.shape) != (times, width):
+                raise ValueError(f"loop step vectors {tuple(loop_step.shape)} != {(times, width)}")
+            self.runs = [(i, 0, False) for i in range(start)]
+            for t in range(times):
+                self.runs += [(i, t, i == start) for i in range(start, stop)]
+            self.runs += [(i, 0, False) for i in range(stop, n)]
 
-    # what the session has to provide
+    # what the session has to provide: one pool / state per (layer, pass)
     def cache_layers(self):
-        return {l["mixer"].index: l["mixer"].cache_entry for l in self.layers
-                if isinstance(l["mixer"], LatentAttention) and l["mixer"].owns_cache}
+        return {(i, t): self.layers[i]["mixer"].cache_entries()["own"] for i, t, _ in self.runs
+                if self.layers[i]["mixer"].cache_entries()}
 
     def state_layers(self):
-        return {l["mixer"].index: (l["mixer"].taps, l["mixer"].channels) for l in self.layers
-                if isinstance(l["mixer"], GatedLinearRecurrence)}
+        return {(i, t): self.layers[i]["mixer"].conv_state() for i, t, _ in self.runs
+                if self.layers[i]["mixer"].conv_state() is not None}
+
+    def _sublayer(self, x, f, pre, post):
+        h = x if pre is None else ops.rmsnorm_rows(x, pre, self.eps, self.norm_offset, out_dtype=self.dtype)
+        y = f(h)
+        if post is None:
+            raise NotImplementedError("a sublayer whose output is added without a norm")
+        ops.rmsnorm_rows(y, post, self.eps, self.norm_offset, out=x, accumulate=True, out_scale=self.residual_mult)
 
     def forward(self, ctx, on_layer=None):
+        """-> the fp32 residual stream after the last layer; ``on_layer(run, x)`` sees it after every layer run."""
         x = ops.embed_scaled(self.embed, ctx.batch.tok_ids, self.embed_scale)
-        for i, l in enumerate(self.layers):
-            ops.rmsnorm_rows(l["mixer"].forward(x, ctx), l["norm1"], self.eps, self.norm_offset, out=x, accumulate=True)
+        for run, (i, t, first) in enumerate(self.runs):
+            l = self.layers[i]
+            if first and self.loop_step is not None:
+                ops.add_row_vector(x, self.loop_step[t])
+            self._sublayer(x, lambda h: l["mixer"].forward(h, ctx, t), l["pre1"], l["post1"])
             if l["mlp"] is not None:
-                ops.rmsnorm_rows(l["mlp"].forward(x, ctx), l["norm2"], self.eps, self.norm_offset, out=x, accumulate=True)
+                self._sublayer(x, lambda h: l["mlp"].forward(h, ctx), l["pre2"], l["post2"])
             if on_layer is not None:
-                on_layer(i, x)
+                on_layer(run, x)
         return x
 
     def logits(self, x, rows_idx):
         h = ops.rmsnorm_rows(x, self.final_norm, self.eps, self.norm_offset, out_dtype=self.dtype, rows_idx=rows_idx)
-        return ops.linear(h, self.head, out_dtype=torch.float32)
+        z = ops.linear(h, self.head, out_dtype=torch.float32)
+        return ops.tanh_cap(z, self.logit_cap) if self.logit_cap > 0 else z

@@ -64,7 +64,7 @@ def build_zobasun(config: dict, tensors: dict, dtype=torch.bfloat16, device="cud
             if f.get("kind", "dense") != "dense":
                 raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
             mlp = ClampedGatedMLP(w_gate=t(p + "mlp.gate"), w_up=t(p + "mlp.up"), w_down=t(p + "mlp.down"), limit=f["limit"])
-        layers.append({"mixer": mixer, "norm1": t(p + "norm1"), "mlp": mlp, "norm2": t(p + "norm2") if mlp else None})
+        layers.append({"mixer": mixer, "post1": t(p + "norm1"), "mlp": mlp, "post2": t(p + "norm2") if mlp else None})
     return LayerStackModel(vocab=int(config["vocab"]), width=int(config["width"]), dtype=dtype, embed=t("embed"),
                            embed_scale=config["embedding"]["scale"], layers=layers, final_norm=t("final.norm"),
                            head=t("head"), eps=eps, norm_offset=1.0)

@@ -343,7 +343,7 @@ def gemm_tc_swiglu(kind, x, w_gate_up, *, sc=None, sr=None):
 from ._lib import ragged_lib as _rl  # noqa: E402
 
 DT_F32, DT_BF16 = 1, 2
-ACT_NONE, ACT_GELU_TANH = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 3
 COMPUTE_AUTO, COMPUTE_FMA32 = 0, 1
 # rows from which a bf16 projection goes to the tcgen05 kernel; below, the streaming GEMV (<= 8 rows) or the warp-MMA tiles
 TC_MIN_ROWS = 17
@@ -430,8 +430,10 @@ def embed_scaled(table, ids, scale):
     return out
 
 
-def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=False, rows_idx=None, cols=None):
-    """RMS norm of fp32 rows (``cols`` leading columns of each); accumulate=True adds the result into fp32 ``out``."""
+def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=False, rows_idx=None, cols=None,
+                 out_scale=1.0):
+    """RMS norm of fp32 rows (``cols`` leading columns of each), times ``out_scale``; accumulate=True adds the result into
+    fp32 ``out``."""
     _chk_dev(x, w, out, rows_idx)
     cols = x.shape[1] if cols is None else cols
     rows = x.shape[0] if rows_idx is None else rows_idx.numel()
@@ -440,8 +442,8 @@ def rmsnorm_rows(x, w, eps, w_offset=0.0, out=None, out_dtype=None, accumulate=F
     if out is None:
         out = torch.empty((rows, cols), dtype=out_dtype or torch.float32, device=x.device)
     check(_rl.tb_rmsnorm_rows(_p(out), _dt(out), out.stride(0), _p(x), x.stride(0), _p(w), _dt(w) if w is not None else 0,
-                              float(w_offset), float(eps), _p(rows_idx), rows, cols, int(accumulate), _stream()),
-          "tb_rmsnorm_rows")
+                              float(w_offset), float(eps), _p(rows_idx), rows, cols, int(accumulate), float(out_scale),
+                              _stream()), "tb_rmsnorm_rows")
     return out
 
 
@@ -470,10 +472,13 @@ def gated_act(gu, out_dtype, alpha, limit, up_shift):
     return out
 
 
-def rope_table(tok_pos, dims, base):
+def rope_table(tok_pos, dims, base, scaling=None):
+    """cos / sin per row and rotary pair; ``scaling`` = (factor, low, high, original) slows the long wavelengths."""
     _chk_dev(tok_pos)
     out = torch.empty((tok_pos.numel(), dims // 2, 2), dtype=torch.float32, device=tok_pos.device)
-    check(_rl.tb_rope_table(_p(out), _p(tok_pos), tok_pos.numel(), dims, float(base), _stream()), "tb_rope_table")
+    factor, low, high, original = scaling or (0.0, 0.0, 0.0, 0.0)
+    check(_rl.tb_rope_table_scaled(_p(out), _p(tok_pos), tok_pos.numel(), dims, float(base), float(factor), float(low),
+                                   float(high), float(original), _stream()), "tb_rope_table_scaled")
     return out
 
 
@@ -519,7 +524,7 @@ def causal_conv1d(x, w, bias, state, batch):
     check(_rl.tb_causal_conv1d(_p(out), _p(x), _p(w), _p(bias), _dt(w), _p(state), _p(batch.tok_seq), _p(batch.tok_pos),
                                _p(batch.seq_start), _p(batch.seq_past), _p(batch.seq_slot), rows, ch, taps, _stream()),
           "tb_causal_conv1d")
-    check(_rl.tb_causal_conv1d_update(_p(state), _p(x), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
+    check(_rl.tb_causal_conv1d_update(_p(state), _p(x), x.stride(0), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
                                       _p(batch.seq_slot), batch.num_seqs, ch, taps, _stream()), "tb_causal_conv1d_update")
     return out
 
@@ -533,6 +538,109 @@ def rglru_scan(u, gates, lam, y, state, batch, blocks, c):
     check(_rl.tb_rglru_scan(_p(out), _dt(out), _p(u), _p(gates), _p(lam), _dt(lam), _p(y), _p(state), _p(batch.seq_start),
                             _p(batch.seq_len), _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, u.shape[1], blocks,
                             float(c), batch.max_len, _p(ws), _stream()), "tb_rglru_scan")
+    return out
+
+
+def add_row_vector(x, vec):
+    """x[r, :] += vec, in place on the fp32 residual stream."""
+    _chk_cuda(x, vec)
+    check(_rl.tb_add_row_vector(_p(x), x.stride(0), _p(vec), _dt(vec), x.shape[0], x.shape[1], _stream()), "tb_add_row_vector")
+    return x
+
+
+def tanh_cap(x, cap):
+    """x <- cap * tanh(x / cap) in place (contiguous fp32)."""
+    _chk_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("tanh_cap works in place on contiguous fp32")
+    check(_rl.tb_tanh_cap(_p(x), x.numel(), float(cap), _stream()), "tb_tanh_cap")
+    return x
+
+
+def qkv_conv_rope_append(proj, conv_w, state, table, dims, pool, batch, page, heads, kv_heads, dim, vdim):
+    """Projected rows (fp32 [N, >= C], q | k | v) -> short causal convolution -> rotation of q and k -> queries
+    [N, heads, dim] in the pool's type, keys and values into the pages; then the carried inputs move on."""
+    _chk_dev(proj, conv_w, state, table, pool)
+    rows, taps = proj.shape[0], conv_w.shape[1]
+    C = heads * dim + kv_heads * (dim + vdim)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < C or conv_w.shape[0] != C or not conv_w.is_contiguous():
+        raise ValueError("qkv_conv_rope_append: proj fp32 [N, >= C], conv_w [C, taps] contiguous")
+    q = torch.empty((rows, heads, dim), dtype=pool.dtype, device=proj.device)
+    check(_rl.tb_qkv_conv_rope_append(_p(q), _p(pool), _dt(pool), _p(proj), proj.stride(0), _p(conv_w), _dt(conv_w),
+                                      _p(state), _p(table), dims, _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.seq_start),
+                                      _p(batch.seq_past), _p(batch.seq_slot), _p(batch.block_table), batch.max_blocks, page,
+                                      rows, heads, kv_heads, dim, vdim, taps, _stream()), "tb_qkv_conv_rope_append")
+    if taps > 1:
+        check(_rl.tb_causal_conv1d_update(_p(state), _p(proj), proj.stride(0), _p(batch.seq_start), _p(batch.seq_len),
+                                          _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, C, taps, _stream()),
+              "tb_causal_conv1d_update")
+    return q
+
+
+def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=None, gate=None):
+    """Grouped-query attention of every row over the last ``window`` cached positions of its sequence (0: all), with an
+    optional softmax sink per head and an optional per-head sigmoid gate (fp32 logits [N, >= heads], any row stride)."""
+    _chk_cuda(q, pool, sink)
+    _chk_dev(gate)
+    rows, heads, dim = q.shape
+    out = torch.empty((rows, heads, vdim), dtype=q.dtype, device=q.device)
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise ValueError("gate logits are fp32 with unit inner stride")
+    check(_rl.tb_window_attention(_p(out), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0,
+                                  _p(sink), _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos),
+                                  _p(batch.block_table), batch.max_blocks, page, rows, heads, kv_heads, dim, vdim,
+                                  float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, _stream()),
+          "tb_window_attention")
+    return out
+
+
+MOE_TILE = 64
+
+
+def moe_route(logits, correction, top, groups, keep):
+    """-> (ids int32 [N, top], weights fp32 [N, top]) from fp32 router logits [N, experts]."""
+    _chk_cuda(logits, correction)
+    rows, experts = logits.shape
+    ids = torch.empty((rows, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((rows, top), dtype=torch.float32, device=logits.device)
+    check(_rl.tb_moe_route(_p(ids), _p(weights), _p(logits.contiguous()), _p(correction),
+                           _dt(correction) if correction is not None else 0, rows, experts, top, groups, keep, _stream()),
+          "tb_moe_route")
+    return ids, weights
+
+
+def moe_plan(ids, experts):
+    """-> (slot_pair int32 [tiles * MOE_TILE], tile_expert int32 [tiles]): the pairs sorted by expert in whole tiles."""
+    _chk_cuda(ids)
+    pairs = ids.numel()
+    tiles = _rl.tb_moe_plan_tiles(pairs, experts, MOE_TILE)
+    slot_pair = torch.empty((tiles * MOE_TILE,), dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty((tiles,), dtype=torch.int32, device=ids.device)
+    check(_rl.tb_moe_plan(_p(slot_pair), _p(tile_expert), _p(ids), pairs, experts, MOE_TILE, tiles, _stream()), "tb_moe_plan")
+    return slot_pair, tile_expert
+
+
+def moe_linear(a, w, slot_pair, tile_expert, *, a_div, c_rows, out_dtype, act=ACT_NONE, compute=COMPUTE_AUTO):
+    """Expert products over a plan.  w [experts, N, K].  a_div > 0: ``a`` holds token rows and slot s reads row
+    slot_pair[s] // a_div; a_div == 0: ``a`` holds one row per slot.  c_rows == 0: the result has one row per slot;
+    c_rows > 0: that many rows, row = the pair's index."""
+    _chk_dev(a, w, slot_pair, tile_expert)
+    _, N, K = w.shape
+    if not w.is_contiguous() or a.stride(1) != 1 or a.shape[1] != K:
+        raise ValueError("moe_linear: w [experts, N, K] contiguous, a [*, K]")
+    out = torch.empty((c_rows or slot_pair.numel(), N), dtype=out_dtype, device=a.device)
+    check(_rl.tb_moe_linear(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w), _dt(w), _p(slot_pair),
+                            _p(tile_expert), tile_expert.numel(), int(a_div), int(c_rows > 0), N, K, act, compute, _stream()),
+          "tb_moe_linear")
+    return out
+
+
+def moe_combine(y, weights):
+    """out[n] = sum_k weights[n, k] * y[n * top + k]  (fp32)."""
+    _chk_cuda(y, weights)
+    rows, top = weights.shape
+    out = torch.empty((rows, y.shape[1]), dtype=torch.float32, device=y.device)
+    check(_rl.tb_moe_combine(_p(out), _p(y), _p(weights), rows, y.shape[1], top, _stream()), "tb_moe_combine")
     return out
 
 
