@@ -65,6 +65,14 @@ int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const float* x, int64
                     float w_offset, float eps, const int* rows_idx, int rows, int cols, int accumulate, float out_scale,
                     tb_stream_t stream);
 
+/* The residual step of a layer that normalises before AND after its sublayers, with the next sublayer's input, in one
+ * pass: x <- x + out_scale * y / rms(y) * (w_post + w_offset), then h = x / rms(x) * (w_pre + w_offset) stored as h_dtype.
+ * x fp32 in place (row stride ldx), y fp32 (ldy); both weights of type w_dtype.  Computes what tb_rmsnorm_rows with
+ * accumulate followed by tb_rmsnorm_rows computes. */
+int tb_residual_norm_rows(float* x, int64_t ldx, const float* y, int64_t ldy, const void* w_post, const void* w_pre,
+                          int w_dtype, float w_offset, float eps, float out_scale, void* h, int h_dtype, int64_t ldh, int rows,
+                          int cols, tb_stream_t stream);
+
 /* x[r, :cols] += vec (fp32 rows with stride ld; vec fp32 or bf16): the vector a pass of a looped block of layers adds to
  * the residual stream. */
 int tb_add_row_vector(float* x, int64_t ld, const void* vec, int v_dtype, int rows, int cols, tb_stream_t stream);
@@ -157,11 +165,13 @@ int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* pro
  * out T [N, heads, vdim] = softmax-weighted values, times sigmoid(gate[n, h]) when gate (fp32 logits, row stride ldg) is
  * given.  Softmax in fp32; keys are visited in blocks of 32 absolute positions from the window's first block, so a row's
  * result does not depend on how its prompt was cut or on the batch around it.  vdim <= 256.
- * bf16 with 16 | dim, 16 | vdim, dim and vdim <= 256 runs on tensor cores (tb_window_attention_tensor_cores tells);
- * mode 1 keeps any configuration on the SIMT kernel (A/B). */
+ * bf16 with a (dim, vdim) pair the tensor-core kernel is built for (tb_window_attention_tensor_cores tells) runs on
+ * tensor cores when the per-sequence description is given: seq_start / seq_len / seq_past [seqs] and max_len >= the longest
+ * seq_len (host; it sizes the grid).  mode 1 keeps any configuration on the SIMT kernel (A/B). */
 int tb_window_attention_tensor_cores(int dtype, int heads, int kv_heads, int dim, int vdim);
 int tb_window_attention(void* out, const void* q, const void* pool, int dtype, const float* gate, int64_t ldg,
                         const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos, const int* block_table,
+                        const int* seq_start, const int* seq_len, const int* seq_past, int seqs, int max_len,
                         int max_blocks, int page, int rows, int heads, int kv_heads, int dim, int vdim, float scale,
                         int window, int mode, tb_stream_t stream);
 

@@ -172,11 +172,16 @@ def forward(tokens, P, cfg, trace=None):
 
 
 def random_nililix(layers, *, width=48, vocab=61, eps=1e-5, residual_mult=0.8, logit_softcap=20.0, loop=None, seed=0,
-                   dtype=torch.bfloat16):
+                   dtype=torch.bfloat16, spaced_corrections=False):
     """A small random model.  ``layers``: list of dicts {heads, kv_heads, dim, vdim, conv, [window], [rot_dims], [rot_base],
     [scaling], [scale], [sink], [gate], mlp: None | ("dense", ff) | ("moe", ff, experts, top, groups, keep)}.  ``loop`` =
     (start, stop, times).  Returns (config, tensors) in the checkpoint's naming; values are rounded to ``dtype`` so that
-    product and oracle start from the same numbers."""
+    product and oracle start from the same numbers.
+
+    ``spaced_corrections``: the routers' corrections are 2.5 * 2^k in shuffled order instead of random numbers of the
+    scores' size, so that neither an expert's nor a group's rank can hang on a score (every sum of two corrections differs
+    from every other by more than two scores can): the choice is then the same for every token, and a run in reduced
+    precision can be compared position by position without a close call deciding which experts ran."""
     g = torch.Generator().manual_seed(seed)
 
     def n(*shape, std=None, mean=0.0):
@@ -217,6 +222,8 @@ def random_nililix(layers, *, width=48, vocab=61, eps=1e-5, residual_mult=0.8, l
                 mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}}}
                 # corrections of the size of the scores themselves, some negative: the choice differs from the plain top-k
                 t.update({p + "mlp.router": n(E, width, std=3.0 * width ** -0.5), p + "mlp.correction": n(E, std=0.5, mean=-0.3)})
+                if spaced_corrections:
+                    t[p + "mlp.correction"] = (2.5 * 2.0 ** torch.randperm(E, generator=g).double()).to(dtype)
                 for e in range(E):
                     t.update({f"{p}mlp.e{e}.gate": n(ff, width, std=2.0 * width ** -0.5),
                               f"{p}mlp.e{e}.up": n(ff, width, std=2.0 * width ** -0.5), f"{p}mlp.e{e}.down": n(width, ff)})

@@ -187,6 +187,7 @@ RAGGED_SIGNATURES = {
     "tb_cast_rows_bf16": (i32, [vp, vp, i64, i32, i32, vp]),
     "tb_embed_scaled": (i32, [vp, vp, i32, vp, f32, i32, i32, i32, vp]),
     "tb_rmsnorm_rows": (i32, [vp, i32, i64, vp, i64, vp, i32, f32, f32, vp, i32, i32, i32, f32, vp]),
+    "tb_residual_norm_rows": (i32, [vp, i64, vp, i64, vp, vp, i32, f32, f32, f32, vp, i32, i64, i32, i32, vp]),
     "tb_add_row_vector": (i32, [vp, i64, vp, i32, i32, i32, vp]),
     "tb_tanh_cap": (i32, [vp, i64, f32, vp]),
     "tb_gated_act": (i32, [vp, i32, vp, i32, i32, f32, f32, f32, vp]),
@@ -202,8 +203,8 @@ RAGGED_SIGNATURES = {
     "tb_qkv_conv_rope_append": (i32, [vp, vp, i32, vp, i64, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                       i32, i32, i32, i32, vp]),
     "tb_window_attention_tensor_cores": (i32, [i32, i32, i32, i32, i32]),
-    "tb_window_attention": (i32, [vp, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32,
-                                  i32, vp]),
+    "tb_window_attention": (i32, [vp, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
+                                  i32, i32, f32, i32, i32, vp]),
     "tb_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "tb_moe_plan_tiles": (i32, [i32, i32, i32]),
     "tb_moe_plan": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),

@@ -57,6 +57,46 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(void* out, int out_dt
   }
 }
 
+// Sandwich-normalised residual step and the next sublayer's input in one pass over the row:
+//   x <- x + out_scale * y / rms(y) * (w_post + off);   h = x / rms(x) * (w_pre + off)   (h in its own type)
+// A thread re-reads only what it wrote itself, so the row needs no fence between the passes.
+__global__ void __launch_bounds__(256) residual_norm_rows_kernel(float* x, int64_t ldx, const float* y, int64_t ldy, const void* w_post,
+                                                                 const void* w_pre, int w_dtype, float w_offset, float eps,
+                                                                 float out_scale, void* h, int h_dtype, int64_t ldh, int cols) {
+  __shared__ float red[8];
+  __shared__ float inv_s;
+  const int row = blockIdx.x;
+  const float* yr = y + (int64_t) row * ldy;
+  float* xr = x + (int64_t) row * ldx;
+  auto block_inv = [&](float ss) {
+    ss = warp_sum(ss);
+    __syncthreads();                               // red / inv_s of the previous reduction have been read
+    if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+      v = warp_sum(v);
+      if (threadIdx.x == 0) inv_s = 1.f / sqrtf(v / (float) cols + eps);
+    }
+    __syncthreads();
+    return inv_s;
+  };
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) { const float v = yr[c]; ss = fmaf(v, v, ss); }
+  const float inv_y = block_inv(ss);
+  ss = 0.f;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    float v = yr[c] * inv_y;
+    v *= ld_f(w_post, w_dtype, c) + w_offset;
+    v = xr[c] + v * out_scale;
+    xr[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float inv_x = block_inv(ss);
+  for (int c = threadIdx.x; c < cols; c += 256)
+    st_f(h, h_dtype, (int64_t) row * ldh + c, xr[c] * inv_x * (ld_f(w_pre, w_dtype, c) + w_offset));
+}
+
 __global__ void gated_act_kernel(void* out, int out_dtype, const float* gu, int64_t n, int ff, float alpha, float limit,
                                  float up_shift) {
   for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
@@ -155,6 +195,17 @@ extern "C" int tb_rmsnorm_rows(void* out, int out_dtype, int64_t ldo, const floa
   if (rows == 0) return 0;
   rmsnorm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(out, out_dtype, ldo, x, ldi, w, w_dtype, w_offset, eps,
                                                                rows_idx, cols, accumulate, out_scale);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_residual_norm_rows(float* x, int64_t ldx, const float* y, int64_t ldy, const void* w_post, const void* w_pre,
+                                     int w_dtype, float w_offset, float eps, float out_scale, void* h, int h_dtype, int64_t ldh,
+                                     int rows, int cols, tb_stream_t stream) {
+  if (!x || !y || !w_post || !w_pre || !h || !dt_ok(w_dtype) || !dt_ok(h_dtype) || cols <= 0 || rows < 0) return -1;
+  if (rows == 0) return 0;
+  residual_norm_rows_kernel<<<rows, 256, 0, (cudaStream_t) stream>>>(x, ldx, y, ldy, w_post, w_pre, w_dtype, w_offset, eps,
+                                                                     out_scale, h, h_dtype, ldh, cols);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -13,8 +13,8 @@
 //   window_attention_kernel       any sizes, fp32 or bf16: one CTA per (row, key/value head, 4 query heads of its group);
 //                                 key blocks of 32 positions aligned to absolute positions, from the window's first block,
 //                                 staged as fp32; lane = key for the scores, lane = value column for the weighted sum.
-//   window_attention_mma_kernel   bf16, 16 | dim, 8 | vdim: one CTA per (sequence, key/value head, 16 / group-size query
-//                                 positions ...) — see below.
+//   window_attention_mma_kernel   bf16 and the head sizes it is built for: tensor cores, 64 (token, head) rows of one
+//                                 sequence and key/value head per CTA — see its own comment below.
 //
 // The softmax runs online in fp32 and starts from the sink: m = sink_h, l = 1, no value — so the sink is counted once,
 // unscaled, whatever the number of key blocks.  Keys are visited in an order fixed by the row's position alone.
@@ -176,6 +176,247 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core form (bf16 storage).  One CTA = 64 query rows of ONE sequence and ONE key/value head, where a "row" is a
+// (token, query head of the group) pair, r = token * group + head: the heads that share a key/value head sit side by
+// side in the MMA's M, so a key tile is loaded once for all of them and a generation step of one token still fills
+// `group` rows.  Four warps of 16 rows.  Per key tile of 64 absolute positions (tile index = position / 64):
+//   S [16 x 64] = Q [16 x DIM] . K^T            mma.sync m16n8k16 bf16, fp32 accumulators, fragments through ldmatrix
+//   online softmax in fp32 in registers          window / causal mask per row; starts from the sink (m = sink, l = 1)
+//   O [16 x VDIM] += P [16 x 64] . V             P reused from the S registers as the A operand, V through ldmatrix.trans
+// K and V tiles arrive through a two-stage cp.async ring; positions outside [first visible of the CTA, last position of the
+// CTA] are zero-filled, so nothing unwritten in the pool reaches an accumulator.  A tile that is wholly masked for a row
+// adds exact zeros and rescales by exactly 1, so a row's result does not depend on the rows it shares a CTA with.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t) __cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = (uint32_t) __cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t) __cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;                       // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+constexpr int kMmaRows = 64, kMmaKeys = 64;
+
+struct MmaArgs {
+  AttnArgs a;
+  const int *seq_start, *seq_len, *seq_past;
+};
+
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16* out, const __nv_bfloat16* q,
+                                                                   const __nv_bfloat16* pool, MmaArgs m) {
+  constexpr int LDQ = DIM + 8, LDV = VDIM + 8;        // +16 bytes per row: ldmatrix rows fall into distinct banks
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][LDQ]
+  __nv_bfloat16* ks = qs + kMmaRows * LDQ;                                   // [2][64][LDQ]
+  __nv_bfloat16* vs = ks + 2 * kMmaKeys * LDQ;                               // [2][64][LDV]
+  const AttnArgs& a = m.a;
+  const int e = blockIdx.y, g = blockIdx.z;
+  const int per = a.H / a.G, len = m.seq_len[e], past = m.seq_past[e], row0 = m.seq_start[e];
+  const int r0 = blockIdx.x * kMmaRows;                 // first (token, head) row of this CTA
+  if (r0 >= len * per) return;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gq = lane / 4, tq = lane % 4;
+  const int t_first = r0 / per;
+  const int r_last = min(r0 + kMmaRows, len * per) - 1, t_last = r_last / per;
+  const int p_last = past + t_last;                     // last position any row of the CTA sees
+  const int p_first = past + t_first;
+  const int lo_cta = a.window > 0 && p_first - a.window + 1 > 0 ? p_first - a.window + 1 : 0;
+  const int E = a.G * (DIM + VDIM);
+  const int* bt = a.block_table + (int64_t) e * a.max_blocks;
+
+  // queries of the CTA's rows (zeros for rows past the sequence's portion)
+  for (int i = threadIdx.x; i < kMmaRows * (DIM / 8); i += 128) {
+    const int r = i / (DIM / 8), c = (i % (DIM / 8)) * 8;
+    const int R = r0 + r, t = R / per, hl = R % per;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t < len) v = *reinterpret_cast<const uint4*>(q + ((int64_t) (row0 + t) * a.H + g * per + hl) * DIM + c);
+    *reinterpret_cast<uint4*>(qs + r * LDQ + c) = v;
+  }
+  auto load_tile = [&](int kt, int stage) {
+    const int j0 = kt * kMmaKeys;
+    __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
+    __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
+    for (int i = threadIdx.x; i < kMmaKeys * (DIM / 8); i += 128) {
+      const int jj = i / (DIM / 8), c = (i % (DIM / 8)) * 8, j = j0 + jj;
+      const bool ok = j >= lo_cta && j <= p_last;
+      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / a.page] * a.page + j % a.page) * E + g * DIM + c : pool;
+      cp_async16(kd + jj * LDQ + c, src, ok);
+    }
+    for (int i = threadIdx.x; i < kMmaKeys * (VDIM / 8); i += 128) {
+      const int jj = i / (VDIM / 8), c = (i % (VDIM / 8)) * 8, j = j0 + jj;
+      const bool ok = j >= lo_cta && j <= p_last;
+      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / a.page] * a.page + j % a.page) * E + a.G * DIM + g * VDIM + c : pool;
+      cp_async16(vd + jj * LDV + c, src, ok);
+    }
+  };
+  const int kt0 = lo_cta / kMmaKeys, kt1 = p_last / kMmaKeys;
+  load_tile(kt0, 0);
+  cp_async_commit();
+
+  // the two rows of this thread: warp * 16 + gq and + 8
+  int pos_r[2], lo_r[2], head_r[2];
+  bool live_r[2];
+  float m_r[2], l_r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int R = r0 + warp * 16 + gq + h * 8, t = R / per;
+    live_r[h] = t < len;
+    head_r[h] = g * per + R % per;
+    pos_r[h] = live_r[h] ? past + t : -1;               // a dead row sees nothing
+    lo_r[h] = a.window > 0 && pos_r[h] - a.window + 1 > 0 ? pos_r[h] - a.window + 1 : 0;
+    m_r[h] = -INFINITY;
+    l_r[h] = 0.f;
+    // the sink: a term exp(sink - m) of the denominator without a value; one thread of the row's quad carries it
+    if (a.sink && live_r[h]) { m_r[h] = ld_w(a.sink, a.sink_dtype, head_r[h]) * 1.4426950408889634f; l_r[h] = tq == 0 ? 1.f : 0.f; }
+  }
+  const float scale2 = a.scale * 1.4426950408889634f;   // scores in units of log 2: exp2f below
+  float o[VDIM / 8][4];
+#pragma unroll
+  for (int n = 0; n < VDIM / 8; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+  __syncthreads();                                      // qs is written
+  uint32_t qf[DIM / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < DIM / 16; ++kk)
+    ldsm_x4(qf[kk], qs + (warp * 16 + lane % 16) * LDQ + kk * 16 + (lane / 16) * 8);
+
+  for (int kt = kt0; kt <= kt1; ++kt) {
+    const int stage = (kt - kt0) & 1;
+    if (kt < kt1) load_tile(kt + 1, stage ^ 1);         // the other stage was consumed before the barrier that ended kt - 1
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
+    const __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
+    const int j0 = kt * kMmaKeys;
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < DIM / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {                  // two key groups of 8 per ldmatrix.x4
+        uint32_t b[4];
+        ldsm_x4(b, kd + (np * 16 + lane % 8 + (lane / 16) * 8) * LDQ + kk * 16 + ((lane / 8) % 2) * 8);
+        mma_bf16_16816(s[2 * np], qf[kk], b[0], b[1]);
+        mma_bf16_16816(s[2 * np + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int h = c >> 1, j = j0 + n * 8 + 2 * tq + (c & 1);
+        const float v = (j >= lo_r[h] && j <= pos_r[h]) ? s[n][c] * scale2 : -INFINITY;
+        s[n][c] = v;
+        mx[h] = fmaxf(mx[h], v);
+      }
+    float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_r[h], mx[h]);
+      corr[h] = m_new == -INFINITY ? 1.f : exp2f(m_r[h] - m_new);     // nothing seen yet: nothing to rescale
+      m_r[h] = m_new;
+      mx[h] = m_new == -INFINITY ? 0.f : m_new;                       // exp2f(-inf - 0) = 0 below
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float p = exp2f(s[n][c] - mx[c >> 1]);
+        s[n][c] = p;
+        rs[c >> 1] += p;
+      }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_r[h] = l_r[h] * corr[h] + rs[h];    // per-thread partial sums; the quad is added at the end
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int np = 0; np < VDIM / 16; ++np) {
+        uint32_t b[4];
+        ldsm_x4_trans(b, vd + (kk * 16 + lane % 8 + ((lane / 8) % 2) * 8) * LDV + np * 16 + (lane / 16) * 8);
+        mma_bf16_16816(o[2 * np], pa, b[0], b[1]);
+        mma_bf16_16816(o[2 * np + 1], pa, b[2], b[3]);
+      }
+    }
+    __syncthreads();                                    // this stage may be overwritten by the load issued next trip
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float l = l_r[h];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    l_r[h] = l;
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (!live_r[h]) continue;
+    const int R = r0 + warp * 16 + gq + h * 8, t = R / per;
+    float f = 1.f / l_r[h];
+    if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) (row0 + t) * a.ldg + head_r[h]]));
+    __nv_bfloat16* dst = out + ((int64_t) (row0 + t) * a.H + head_r[h]) * VDIM;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n)
+      *reinterpret_cast<__nv_bfloat162*>(dst + n * 8 + 2 * tq) = __floats2bfloat162_rn(o[n][2 * h] * f, o[n][2 * h + 1] * f);
+  }
+}
+
+template <int DIM, int VDIM>
+int launch_window_mma(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat16* pool, const MmaArgs& m, int seqs,
+                      int max_len, cudaStream_t s) {
+  constexpr size_t smem = ((size_t) kMmaRows * (DIM + 8) + 2 * kMmaKeys * (DIM + 8) + 2 * kMmaKeys * (VDIM + 8)) * 2;
+  static bool raised = false;
+  if (!raised && smem > 48 * 1024) {
+    TB_CHECK_CUDA(cudaFuncSetAttribute(window_attention_mma_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+    raised = true;
+  }
+  const int per = m.a.H / m.a.G;
+  dim3 grid(((int64_t) max_len * per + kMmaRows - 1) / kMmaRows, seqs, m.a.G);
+  window_attention_mma_kernel<DIM, VDIM><<<grid, 128, smem, s>>>(out, q, pool, m);
+  return 0;
+}
+
+// the (dim, vdim) pairs the tensor-core kernel is built for
+#define TB_WINDOW_MMA_SHAPES(X) X(32, 16) X(32, 32) X(64, 32) X(64, 64) X(96, 96) X(128, 64) X(128, 128)
+
 }  // namespace
 }  // namespace tb
 
@@ -204,13 +445,17 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
 }
 
 extern "C" int tb_window_attention_tensor_cores(int dtype, int heads, int kv_heads, int dim, int vdim) {
-  (void) dtype; (void) heads; (void) kv_heads; (void) dim; (void) vdim;
+  if (dtype != TB_DT_BF16 || heads <= 0 || kv_heads <= 0 || heads % kv_heads) return 0;
+#define X(D, V) if (dim == D && vdim == V) return 1;
+  TB_WINDOW_MMA_SHAPES(X)
+#undef X
   return 0;
 }
 
 extern "C" int tb_window_attention(void* out, const void* q, const void* pool, int dtype, const float* gate, int64_t ldg,
                                    const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos,
-                                   const int* block_table, int max_blocks, int page, int rows, int heads, int kv_heads,
+                                   const int* block_table, const int* seq_start, const int* seq_len, const int* seq_past,
+                                   int seqs, int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
                                    int dim, int vdim, float scale, int window, int mode, tb_stream_t stream) {
   if (!out || !q || !pool || !tok_seq || !tok_pos || !block_table) return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
@@ -221,10 +466,24 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
   if (rows == 0) return 0;
   AttnArgs a{gate, ldg, sink, sink_dtype, tok_seq, tok_pos, block_table, max_blocks, page, heads, kv_heads, dim, vdim,
              window, scale};
+  cudaStream_t s = (cudaStream_t) stream;
+  if (mode == 0 && seq_start && seq_len && seq_past && seqs > 0 && max_len > 0 && seqs <= 65535 &&
+      tb_window_attention_tensor_cores(dtype, heads, kv_heads, dim, vdim) && (uintptr_t) q % 16 == 0 && (uintptr_t) pool % 16 == 0) {
+    MmaArgs m{a, seq_start, seq_len, seq_past};
+#define X(D, V)                                                                                                     \
+  if (dim == D && vdim == V) {                                                                                      \
+    const int rc = launch_window_mma<D, V>((__nv_bfloat16*) out, (const __nv_bfloat16*) q, (const __nv_bfloat16*) pool, m, \
+                                           seqs, max_len, s);                                                       \
+    if (rc) return rc;                                                                                              \
+  }
+    TB_WINDOW_MMA_SHAPES(X)
+#undef X
+    TB_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   const size_t smem = ((size_t) kTile * (dim + 1) + (size_t) kTile * vdim + (size_t) kWarps * dim) * sizeof(float);
   if (smem > 220 * 1024) return -2;
   dim3 grid(rows, kv_heads, (heads / kv_heads + kWarps - 1) / kWarps);
-  cudaStream_t s = (cudaStream_t) stream;
   static size_t raised_f = 48 * 1024, raised_b = 48 * 1024;
   if (dtype == TB_DT_F32) {
     if (smem > raised_f) {

@@ -263,25 +263,37 @@ class LayerStackModel:
         return {(i, t): self.layers[i]["mixer"].conv_state() for i, t, _ in self.runs
                 if self.layers[i]["mixer"].conv_state() is not None}
 
-    def _sublayer(self, x, f, pre, post):
-        h = x if pre is None else ops.rmsnorm_rows(x, pre, self.eps, self.norm_offset, out_dtype=self.dtype)
-        y = f(h)
-        if post is None:
-            raise NotImplementedError("a sublayer whose output is added without a norm")
-        ops.rmsnorm_rows(y, post, self.eps, self.norm_offset, out=x, accumulate=True, out_scale=self.residual_mult)
-
     def forward(self, ctx, on_layer=None):
-        """-> the fp32 residual stream after the last layer; ``on_layer(run, x)`` sees it after every layer run."""
+        """-> the fp32 residual stream after the last layer; ``on_layer(run, x)`` sees it after every layer run.
+
+        Each sublayer is x <- x + residual_mult * norm_post(f(norm_pre(x))).  Where the next sublayer has a norm on its
+        input and nothing is added to x in between, its input comes out of the same kernel as this sublayer's residual
+        update (``ops.residual_norm_rows``)."""
         x = ops.embed_scaled(self.embed, ctx.batch.tok_ids, self.embed_scale)
+        subs = []                                   # (function of h, pre weight, post weight, step vector, run if it ends one)
         for run, (i, t, first) in enumerate(self.runs):
             l = self.layers[i]
-            if first and self.loop_step is not None:
-                ops.add_row_vector(x, self.loop_step[t])
-            self._sublayer(x, lambda h: l["mixer"].forward(h, ctx, t), l["pre1"], l["post1"])
+            step = self.loop_step[t] if first and self.loop_step is not None else None
+            subs.append((lambda h, l=l, t=t: l["mixer"].forward(h, ctx, t), l["pre1"], l["post1"], step, None if l["mlp"] else run))
             if l["mlp"] is not None:
-                self._sublayer(x, lambda h: l["mlp"].forward(h, ctx), l["pre2"], l["post2"])
-            if on_layer is not None:
-                on_layer(run, x)
+                subs.append((lambda h, l=l: l["mlp"].forward(h, ctx), l["pre2"], l["post2"], None, run))
+        h = None
+        for k, (f, pre, post, step, ends_run) in enumerate(subs):
+            if step is not None:
+                ops.add_row_vector(x, step)
+            if h is None:
+                h = x if pre is None else ops.rmsnorm_rows(x, pre, self.eps, self.norm_offset, out_dtype=self.dtype)
+            y = f(h)
+            if post is None:
+                raise NotImplementedError("a sublayer whose output is added without a norm")
+            nxt = subs[k + 1] if k + 1 < len(subs) else None
+            if nxt is not None and nxt[1] is not None and nxt[3] is None and nxt[1].dtype == post.dtype:
+                h = ops.residual_norm_rows(x, y, post, nxt[1], self.eps, self.norm_offset, self.residual_mult, self.dtype)
+            else:
+                ops.rmsnorm_rows(y, post, self.eps, self.norm_offset, out=x, accumulate=True, out_scale=self.residual_mult)
+                h = None
+            if ends_run is not None and on_layer is not None:
+                on_layer(ends_run, x)
         return x
 
     def logits(self, x, rows_idx):

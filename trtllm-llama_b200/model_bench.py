@@ -1,5 +1,5 @@
-"""``bench.py --model zobasun``: prefill and decode throughput of the in-flight served design at layer sizes that resemble
-real models (random bf16 weights), beside a LLaMA engine of equal width / depth / feed-forward size served by
+"""``bench.py --model zobasun | nililix``: prefill and decode throughput of an in-flight served design at layer sizes that
+resemble real models (random bf16 weights), beside a LLaMA engine of equal width / depth / feed-forward size served by
 ``GenerationSession`` (fp16), and every operator's distance from its roofline.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs; every timed run works on tensors far larger than L2 or is
@@ -54,11 +54,56 @@ def random_zobasun(torch, s, seed=0):
     return cfg, t
 
 
+NILILIX_SIZES = {
+    # attention: heads x dim over kv_heads, window; feed-forward: dense ff, or `experts` experts of eff with `top` active
+    # (top * eff = ff, so a routed layer does the dense layer's work per token)
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=512, rot_dims=64, ff=5632, experts=16, top=4,
+                  eff=1408, groups=4, keep=2, vocab=32000),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, rot_dims=64, ff=11008, experts=16, top=4,
+                  eff=2752, groups=4, keep=2, vocab=32000),
+}
+
+
+def random_nililix(torch, s, seed=0):
+    """config + bf16 tensors of a 4-layer stack [dense, routed, dense, routed] whose middle two layers run twice."""
+    g = torch.Generator().manual_seed(seed)
+    W, H, G, d, dv = s["width"], s["heads"], s["kv_heads"], s["dim"], s["vdim"]
+
+    def n(*shape, std=None):
+        std = std if std is not None else shape[-1] ** -0.5
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    mixer = dict(heads=H, kv_heads=G, dim=d, vdim=dv, conv=4, scale=d ** -0.5, mask=dict(size=s["window"]),
+                 rot=dict(base=500000.0, dims=s["rot_dims"], scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    dense = dict(kind="dense", ff=s["ff"])
+    moe = dict(kind="moe", expert=dict(ff=s["eff"]),
+               router=dict(experts=s["experts"], top=s["top"], groups=dict(count=s["groups"], keep=s["keep"])))
+    layers = [dict(type="attention", mixer=mixer, mlp=m) for m in (dense, moe, dense, moe)]
+    cfg = dict(architecture="Nililix", vocab=s["vocab"], width=W, norm=dict(eps=1e-6), residual_mult=0.7, logit_softcap=30.0,
+               loop=dict(start=1, stop=3, times=2), layers=layers)
+    t = {"embed": n(s["vocab"], W, std=1.0), "head": n(s["vocab"], W), "final.norm": n(W, std=0.1) + 1, "loop.step": n(2, W, std=0.1)}
+    for i, l in enumerate(layers):
+        p = f"l{i}."
+        for k in ("norm1", "norm1b", "norm2", "norm2b"):
+            t[p + k] = n(W, std=0.1) + 1
+        t.update({p + "mix.q": n(H * d, W), p + "mix.k": n(G * d, W), p + "mix.v": n(G * dv, W), p + "mix.q.conv": n(H * d, 4, std=0.5),
+                  p + "mix.k.conv": n(G * d, 4, std=0.5), p + "mix.v.conv": n(G * dv, 4, std=0.5), p + "mix.sink": n(H, std=1.0),
+                  p + "mix.g": n(H, W), p + "mix.o": n(W, H * dv)})
+        if l["mlp"]["kind"] == "dense":
+            t.update({p + "mlp.up": n(s["ff"], W), p + "mlp.down": n(W, s["ff"])})
+        else:
+            t.update({p + "mlp.router": n(s["experts"], W), p + "mlp.correction": n(s["experts"], std=0.1)})
+            for e in range(s["experts"]):
+                t.update({f"{p}mlp.e{e}.gate": n(s["eff"], W), f"{p}mlp.e{e}.up": n(s["eff"], W), f"{p}mlp.e{e}.down": n(W, s["eff"])})
+    return cfg, t
+
+
 class OpTimer:
     """Wraps the ragged operators of ``ops`` with CUDA-event timers and the bytes / flops each call moves."""
 
     NAMES = ("linear", "linear_gated", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
-             "latent_attention", "causal_conv1d", "rglru_scan")
+             "latent_attention", "causal_conv1d", "rglru_scan", "qkv_conv_rope_append", "window_attention", "moe_route",
+             "moe_plan", "moe_linear", "moe_combine", "add_row_vector", "tanh_cap")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.rec, self.saved = torch, ops, [], {}
@@ -92,6 +137,31 @@ class OpTimer:
             for s, p in zip(batch._host[batch.num_rows:batch.num_rows * 2].tolist(), pos.tolist()):
                 seqlen[s] = max(seqlen.get(s, 0), p + 1)
             return name, 2.0 * keys * heads * (2 * lat + rot), sum(seqlen.values()) * (lat + rot) * pool.element_size() + nb(qa, out)
+        if name == "window_attention":
+            q, pool, batch, page, G, dv, window = args[0], args[1], args[2], args[3], args[4], args[5], args[7]
+            H, d = q.shape[1], q.shape[2]
+            pos = batch._host[batch.num_rows * 2:batch.num_rows * 3].double()
+            keys = float(((pos + 1).clamp(max=window) if window else (pos + 1)).sum())
+            seq = batch._host[batch.num_rows:batch.num_rows * 2].tolist()
+            first, last = {}, {}
+            for sq, p in zip(seq, pos.tolist()):
+                first[sq] = min(first.get(sq, p), p)
+                last[sq] = max(last.get(sq, p), p)
+            # minimal traffic: the cached positions any row of the sequence sees, once; queries and outputs once
+            seen = sum(last[sq] + 1 - (max(0, first[sq] - window + 1) if window else 0) for sq in first)
+            return name, 2.0 * keys * H * (d + dv), seen * G * (d + dv) * pool.element_size() + nb(q, out)
+        if name == "qkv_conv_rope_append":
+            proj, H, G, d, dv = args[0], args[8], args[9], args[10], args[11]
+            C = H * d + G * (d + dv)
+            return name, 0.0, proj.shape[0] * C * (4 + args[5].element_size())
+        if name == "moe_linear":
+            a, w, slot_pair = args[0], args[1], args[2]
+            pairs = (kw.get("c_rows") or 0) or (a.shape[0] * kw["a_div"] if kw.get("a_div") else 0)
+            self._pairs = pairs or getattr(self, "_pairs", slot_pair.numel())
+            E, N, K = w.shape
+            used = min(E, self._pairs)
+            return f"moe_linear {self._pairs}x{N}x{K} of {E}", 2.0 * self._pairs * N * K, \
+                used * N * K * w.element_size() + self._pairs * (K * a.element_size() + N * out.element_size())
         if name == "latent_kv_append":
             pool, kv, lat, rot = args[0], args[1], args[8], args[9]
             return name, 0.0, kv.shape[0] * (lat + rot) * (4 + pool.element_size())
@@ -166,48 +236,12 @@ def _time(torch, fn, steps, warmup, flush):
     return sorted(ts)[len(ts) // 2]
 
 
-def bench_size(torch, name, steps, warmup, S=2048, B=4):
-    from . import ops
-    from . import runtime as rt
-    from .inflight import InflightSession
-    from .models.zobasun import build_zobasun
-    s, peaks = SIZES[name], _peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    cfg, tensors = random_zobasun(torch, s)
-    model = build_zobasun(cfg, tensors, torch.bfloat16, "cuda")
-    del tensors
-    sess = InflightSession(model, max_tokens=(B + 1) * (S + 64), max_seqs=B + 1)
-    g = torch.Generator().manual_seed(1)
-    prompt = torch.randint(0, s["vocab"], (S,), generator=g).tolist()
-    res = {"size": dict(s), "layers": [l["type"] + ("+kv_from" if "kv_from" in l["mixer"] else "") for l in cfg["layers"]],
-           "prefill_tokens": S, "decode_batch": B, "decode_context": S}
-
-    def prefill():
-        sess.step([("p", prompt, [S - 1])])
-        sess.end("p")
-    t = _time(torch, prefill, steps, warmup, flush)
-    res["prefill_tokens_per_s"] = round(S / t, 1)
-    with OpTimer(torch, ops) as ot:
-        prefill()
-    res["prefill_ops"] = ot.summary(peaks)
-    for b in range(B):
-        sess.step([(("d", b), prompt, [])])
-    dec = [(("d", b), [7 + b], [0]) for b in range(B)]
-    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
-    res["decode_tokens_per_s"] = round(B / t, 1)
-    res["decode_ms_per_step"] = round(t * 1e3, 3)
-    sess.use_cuda_graph = False          # the operators are timed one by one on eager launches
-    with OpTimer(torch, ops) as ot:
-        sess.step(dec)
-    res["decode_ops"] = ot.summary(peaks)
-    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
-    res["decode_ms_per_step_eager"] = round(t * 1e3, 3)
-    del sess, model
-    torch.cuda.empty_cache()
-
+def _llama_side(torch, ops, rt, s, n_layers, res, prompt, S, B, steps, warmup, flush, peaks):
+    """LLaMA (MHA, SwiGLU; fp16) of equal width / depth / feed-forward / vocabulary through ``GenerationSession``, and its
+    like kernels alone.  Fills ``res``; returns (L, engine tensors' gate weight shape) for the caller's own like kernels."""
     # the closest existing model at equal size: LLaMA (MHA, SwiGLU), fp16, same width / depth / feed-forward / vocabulary
     import bench as HB
-    L = {"hidden": s["width"], "inter": s["ff"], "vocab": s["vocab"], "layers": len(cfg["layers"]), "heads": s["width"] // 128}
+    L = {"hidden": s["width"], "inter": s["ff"], "vocab": s["vocab"], "layers": n_layers, "heads": s["width"] // 128}
     mc = rt.ModelConfig(vocab_size=L["vocab"], num_layers=L["layers"], num_heads=L["heads"], hidden_size=L["hidden"],
                         inter_size=L["inter"], max_batch_size=B, max_input_len=S, max_output_len=64)
     lt = rt.build_engine_tensors(HB.make_weights(torch, L, 0, 1), mc)
@@ -253,11 +287,56 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
     like["attention_decode"] = {"us": round(t * 1e6, 1),
                                 "of_roofline": round(B * 2 * H * S * 128 * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     res["llama_like_kernels"] = like
-    del x, xd, qkv, kvc, qd
+    del x, xd, qkv, kvc, qd, ls
+    torch.cuda.empty_cache()
+    return L, tuple(w.shape), fl
+
+
+def bench_size(torch, name, steps, warmup, S=2048, B=4):
+    from . import ops
+    from . import runtime as rt
+    from .inflight import InflightSession
+    from .models.zobasun import build_zobasun
+    s, peaks = SIZES[name], _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cfg, tensors = random_zobasun(torch, s)
+    model = build_zobasun(cfg, tensors, torch.bfloat16, "cuda")
+    del tensors
+    sess = InflightSession(model, max_tokens=(B + 1) * (S + 64), max_seqs=B + 1)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, s["vocab"], (S,), generator=g).tolist()
+    res = {"size": dict(s), "layers": [l["type"] + ("+kv_from" if "kv_from" in l["mixer"] else "") for l in cfg["layers"]],
+           "prefill_tokens": S, "decode_batch": B, "decode_context": S}
+
+    def prefill():
+        sess.step([("p", prompt, [S - 1])])
+        sess.end("p")
+    t = _time(torch, prefill, steps, warmup, flush)
+    res["prefill_tokens_per_s"] = round(S / t, 1)
+    with OpTimer(torch, ops) as ot:
+        prefill()
+    res["prefill_ops"] = ot.summary(peaks)
+    for b in range(B):
+        sess.step([(("d", b), prompt, [])])
+    dec = [(("d", b), [7 + b], [0]) for b in range(B)]
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_tokens_per_s"] = round(B / t, 1)
+    res["decode_ms_per_step"] = round(t * 1e3, 3)
+    sess.use_cuda_graph = False          # the operators are timed one by one on eager launches
+    with OpTimer(torch, ops) as ot:
+        sess.step(dec)
+    res["decode_ops"] = ot.summary(peaks)
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_ms_per_step_eager"] = round(t * 1e3, 3)
+    del sess, model
+    torch.cuda.empty_cache()
+
+    L, w_shape, fl = _llama_side(torch, ops, rt, s, len(cfg["layers"]), res, prompt, S, B, steps, warmup, flush, peaks)
+    H = L["heads"]
     # this design's kernels alone on the same problem sizes (bf16)
     own = {}
     xb = torch.randn(S, L["hidden"], device="cuda").bfloat16()
-    wb = (torch.randn(w.shape[0], w.shape[1], device="cuda") * 0.02).bfloat16()
+    wb = (torch.randn(w_shape[0], w_shape[1], device="cuda") * 0.02).bfloat16()
     t = _time(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
     own["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     xf = torch.randn(B, L["hidden"], device="cuda")
@@ -280,7 +359,77 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
                                "cache_bytes": B * S * (lat + rot) * 2, "llama_cache_bytes": B * 2 * H * S * 128 * 2}
     res["zobasun_like_kernels"] = own
     res["peaks"] = peaks
-    del ls, lt
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_nililix_size(torch, name, steps, warmup, S=2048, B=4):
+    from . import ops
+    from . import runtime as rt
+    from .inflight import InflightSession, RaggedBatch
+    from .models.nililix import build_nililix
+    s, peaks = NILILIX_SIZES[name], _peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    cfg, tensors = random_nililix(torch, s)
+    model = build_nililix(cfg, tensors, torch.bfloat16, "cuda")
+    del tensors
+    sess = InflightSession(model, max_tokens=(B + 1) * (S + 64), max_seqs=B + 1)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, s["vocab"], (S,), generator=g).tolist()
+    res = {"size": dict(s), "layers": [l["mlp"]["kind"] for l in cfg["layers"]], "layer_runs": len(model.runs),
+           "prefill_tokens": S, "decode_batch": B, "decode_context": S}
+
+    def prefill():
+        sess.step([("p", prompt, [S - 1])])
+        sess.end("p")
+    t = _time(torch, prefill, steps, warmup, flush)
+    res["prefill_tokens_per_s"] = round(S / t, 1)
+    with OpTimer(torch, ops) as ot:
+        prefill()
+    res["prefill_ops"] = ot.summary(peaks)
+    for b in range(B):
+        sess.step([(("d", b), prompt, [])])
+    dec = [(("d", b), [7 + b], [0]) for b in range(B)]
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_tokens_per_s"] = round(B / t, 1)
+    res["decode_ms_per_step"] = round(t * 1e3, 3)
+    sess.use_cuda_graph = False          # the operators are timed one by one on eager launches
+    with OpTimer(torch, ops) as ot:
+        sess.step(dec)
+    res["decode_ops"] = ot.summary(peaks)
+    t = _time(torch, lambda: sess.step(dec), steps, warmup, flush)
+    res["decode_ms_per_step_eager"] = round(t * 1e3, 3)
+    del sess, model
+    torch.cuda.empty_cache()
+    # LLaMA with as many layers as this stack RUNS layers (a looped layer counts each time)
+    L, w_shape, fl = _llama_side(torch, ops, rt, s, res["layer_runs"], res, prompt, S, B, steps, warmup, flush, peaks)
+    own = {}
+    xb = torch.randn(S, L["hidden"], device="cuda").bfloat16()
+    wb = (torch.randn(w_shape[0], w_shape[1], device="cuda") * 0.02).bfloat16()
+    t = _time(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
+    own["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    xf = torch.randn(B, L["hidden"], device="cuda")
+    t = _time(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
+    own["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(wb.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
+    H, G, d, dv, win, page = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], 64
+    nblk = -(-S // page)
+    pool = torch.randn((B * nblk * page, G * (d + dv)), device="cuda").bfloat16()
+    sink = torch.zeros(H, device="cuda").bfloat16()
+    pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
+    q = torch.randn(S, H, d, device="cuda").bfloat16()
+    gate = torch.randn(S, H, device="cuda")
+    t = _time(torch, lambda: ops.window_attention(q, pool, pb, page, G, dv, 0.09, win, sink=sink, gate=gate), steps, warmup, flush)
+    keys = sum(min(p + 1, win) for p in range(S))
+    own["attention_prefill"] = {"us": round(t * 1e6, 1), "keys_per_row": round(keys / S, 1),
+                                "of_roofline": round(2.0 * keys * H * (d + dv) / (peaks["bf16_tflops"] * 1e12) / t, 3)}
+    db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
+    qd = q[:B].contiguous()
+    t = _time(torch, lambda: ops.window_attention(qd, pool, db, page, G, dv, 0.09, win, sink=sink, gate=gate[:B]), steps, warmup, flush)
+    cache_bytes = B * min(S, win) * G * (d + dv) * 2
+    own["attention_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(cache_bytes / (peaks["hbm_gbs"] * 1e9) / t, 3),
+                               "cache_bytes": cache_bytes, "llama_cache_bytes": B * 2 * L["heads"] * S * 128 * 2}
+    res["nililix_like_kernels"] = own
+    res["peaks"] = peaks
     torch.cuda.empty_cache()
     return res
 
@@ -289,9 +438,10 @@ def run(args):
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py --model needs a B200 (sm_100a): there is no CPU path")
-    names = args.model_sizes.split(",") if args.model_sizes else list(SIZES)
+    sizes, fn = (NILILIX_SIZES, bench_nililix_size) if args.model == "nililix" else (SIZES, bench_size)
+    names = args.model_sizes.split(",") if args.model_sizes else list(sizes)
     out = {"bench": "model_compare", "model": args.model, "dtype": "bf16 (llama: fp16)", "data": "synthetic",
            "steps": args.steps, "warmup": max(3, args.warmup), "sizes": {}}
     for nm in names:
-        out["sizes"][nm] = bench_size(torch, nm, args.steps, args.warmup)
+        out["sizes"][nm] = fn(torch, nm, args.steps, args.warmup)
     print(json.dumps(out))

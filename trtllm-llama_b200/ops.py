@@ -541,6 +541,19 @@ def rglru_scan(u, gates, lam, y, state, batch, blocks, c):
     return out
 
 
+def residual_norm_rows(x, y, w_post, w_pre, eps, w_offset=0.0, out_scale=1.0, out_dtype=torch.float32):
+    """x += out_scale * rmsnorm(y) * (w_post + w_offset) in place, and returns rmsnorm(x) * (w_pre + w_offset) — the
+    post-norm residual update of one sublayer and the pre-norm input of the next in one kernel."""
+    _chk_dev(x, y, w_post, w_pre)
+    if x.dtype != torch.float32 or y.dtype != torch.float32 or x.stride(1) != 1 or y.stride(1) != 1 or w_post.dtype != w_pre.dtype:
+        raise ValueError("residual_norm_rows: fp32 rows, norm weights of one type")
+    h = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(_rl.tb_residual_norm_rows(_p(x), x.stride(0), _p(y), y.stride(0), _p(w_post), _p(w_pre), _dt(w_post), float(w_offset),
+                                    float(eps), float(out_scale), _p(h), _dt(h), h.stride(0), x.shape[0], x.shape[1], _stream()),
+          "tb_residual_norm_rows")
+    return h
+
+
 def add_row_vector(x, vec):
     """x[r, :] += vec, in place on the fp32 residual stream."""
     _chk_cuda(x, vec)
@@ -588,7 +601,8 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
         raise ValueError("gate logits are fp32 with unit inner stride")
     check(_rl.tb_window_attention(_p(out), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0,
                                   _p(sink), _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos),
-                                  _p(batch.block_table), batch.max_blocks, page, rows, heads, kv_heads, dim, vdim,
+                                  _p(batch.block_table), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
+                                  batch.num_seqs, batch.max_len, batch.max_blocks, page, rows, heads, kv_heads, dim, vdim,
                                   float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, _stream()),
           "tb_window_attention")
     return out
