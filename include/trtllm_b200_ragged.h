@@ -184,19 +184,35 @@ int tb_moe_route(int* ids, float* weights, const float* logits, const void* corr
                  int top, int groups, int keep, tb_stream_t stream);
 /* Plan: the N * top (token, choice) pairs sorted by expert, every expert's range padded to whole tiles of `tile` rows.
  * tb_moe_plan_tiles = the number of tiles that is always enough; slot_pair int32 [max_tiles * tile] (pair index, -1 in
- * the padding), tile_expert int32 [max_tiles] (-1: unused tile). */
+ * the padding), tile_expert int32 [max_tiles] (-1: unused tile), pair_slot int32 [pairs] (the inverse map; may be NULL). */
 enum { TB_MOE_TILE = 64 };
 int tb_moe_plan_tiles(int pairs, int experts, int tile);
-int tb_moe_plan(int* slot_pair, int* tile_expert, const int* ids, int pairs, int experts, int tile, int max_tiles,
-                tb_stream_t stream);
+int tb_moe_plan(int* slot_pair, int* tile_expert, int* pair_slot, const int* ids, int pairs, int experts, int tile,
+                int max_tiles, tb_stream_t stream);
 /* c = act(a w_e^T) tile by tile over the plan (tile height TB_MOE_TILE): w [experts, N, K].  a_div > 0: a [tokens, K] and
  * slot s reads row slot_pair[s] / a_div; a_div == 0: a [slots, K].  c_by_pair != 0: C row = pair index, else the slot.
  * compute as tb_linear (AUTO: tensor cores for bf16 weights). */
 int tb_moe_linear(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
                   const int* slot_pair, const int* tile_expert, int max_tiles, int a_div, int c_by_pair, int N, int K, int act,
                   int compute, tb_stream_t stream);
-/* out fp32 [N, width] = sum_k weights[n, k] * y[n * top + k, :]   (y fp32 [N * top, width], k in index order) */
-int tb_moe_combine(float* out, const float* y, const float* weights, int rows, int width, int top, tb_stream_t stream);
+/* The same products on the 5th-generation tensor cores (the kernel of tb_gemm_tc_bf16), for plans with tiles of 128 rows:
+ * x bf16 [max_tiles * 128, K] contiguous in plan order (tb_moe_gather_rows makes it from token rows), w bf16
+ * [experts, N, K], c fp32 (out_type 1) or bf16 (3) [max_tiles * 128, N] in plan order; 8 | K. */
+int tb_gemm_tc_bf16_grouped(void* c, int out_type, const void* x, const void* w, const int* tile_expert, int max_tiles,
+                            int experts, int act, int N, int K, tb_stream_t stream);
+/* xs bf16 [slots, cols] = x[slot_pair[s] / top, :] (x fp32 or bf16 with row stride ldx; zeros where slot_pair[s] < 0). */
+int tb_moe_gather_rows(void* xs, const void* x, int x_dtype, int64_t ldx, const int* slot_pair, int slots, int top, int cols,
+                       tb_stream_t stream);
+/* Expert products for few pairs (generation steps) without a plan: pair b = one row of the streaming kernel against the
+ * weights of expert ids[b].  a_div > 0: a [tokens, K], pair b reads row b / a_div; a_div == 0: a [pairs, K].  c [pairs, N].
+ * act TB_ACT_GATED: w [experts, 2 N, K] (gate rows, then up rows), c = g * sigmoid(alpha g) * (u + up_shift).
+ * Returns -3 when the streaming kernel does not take the shape (bf16 weights, 8 | K, 16-byte aligned rows). */
+int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
+                const int* ids, int pairs, int a_div, int N, int K, int act, float alpha, float up_shift, tb_stream_t stream);
+/* out fp32 [N, width] = sum_k weights[n, k] * y[r(n * top + k), :], k in index order; r(p) = pair_slot[p] (rows of y in
+ * plan order) or p itself when pair_slot is NULL (y fp32 in pair order). */
+int tb_moe_combine(float* out, const float* y, const float* weights, const int* pair_slot, int rows, int width, int top,
+                   tb_stream_t stream);
 
 #ifdef __cplusplus
 }

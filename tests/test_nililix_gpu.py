@@ -148,10 +148,15 @@ def test_router_masks_with_minus_infinity_not_zero():
     assert torch.allclose(w.cpu().sort().values, torch.sigmoid(torch.tensor([-2.2, -2.0])), atol=1e-6)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n", [1, 5, 150])
-def test_routed_experts_alone(dtype, n):
+@pytest.mark.parametrize("dtype,tiles", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)],
+                         ids=["fp32-fma-tiles", "bf16-streaming-or-tcgen05", "bf16-warp-mma-tiles"])
+@pytest.mark.parametrize("n", [1, 5, 40, 150, 700])
+def test_routed_experts_alone(dtype, n, tiles, monkeypatch):
+    """Every form of the expert products: fp32 FMA tiles, bf16 warp-MMA tiles, one streaming product per pair (few
+    tokens), tcgen05 tiles over a plan of 128-row tiles (many)."""
+    from trtllm_llama_b200 import ops
     from trtllm_llama_b200.layers import RoutedExpertsMLP
+    monkeypatch.setattr(ops, "FORCE_TILE_LINEAR", tiles)
     g = torch.Generator().manual_seed(n)
     W, ff, E = 40, 24, 6
     r = lambda *s, std: (torch.randn(*s, generator=g) * std).to(dtype)

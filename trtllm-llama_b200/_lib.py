@@ -207,9 +207,12 @@ RAGGED_SIGNATURES = {
                                   i32, i32, f32, i32, i32, vp]),
     "tb_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "tb_moe_plan_tiles": (i32, [i32, i32, i32]),
-    "tb_moe_plan": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "tb_moe_plan": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+    "tb_gemm_tc_bf16_grouped": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, vp]),
+    "tb_moe_gather_rows": (i32, [vp, vp, i32, i64, vp, i32, i32, i32, vp]),
+    "tb_moe_gemv": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, i32, i32, i32, i32, i32, f32, f32, vp]),
     "tb_moe_linear": (i32, [vp, i32, i64, vp, i32, i64, vp, i32, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp]),
-    "tb_moe_combine": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "tb_moe_combine": (i32, [vp, vp, vp, vp, i32, i32, i32, vp]),
 }
 SIGNATURES.update(RAGGED_SIGNATURES)
 # what libtrtllm_b200_ragged.so exports (csrc/Makefile target `ragged`): the operators above plus the sampling, arg-max

@@ -49,6 +49,8 @@ struct GemmTcParams {
   int M, N, K;
   int n_tiles, m_tiles, splits, kb_total, kb_per_split;
   int band;                // m-tiles per L2 band (rasterisation, see item_coords)
+  const int* tile_expert;  // grouped (routed experts, bf16): m-tile -> expert whose [N, K] block of W it multiplies; < 0: skip the tile
+  int experts;             // grouped: W is [experts * N, K]
   float* partial;          // [items][NT][128] fp32 (int32 bit patterns for KIND 1)
   int* counters;           // [n_tiles * m_tiles]
 };
@@ -143,6 +145,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       for (int it = blockIdx.x; it < items; it += gridDim.x) {
         int nt, mt, split;
         item_coords(p, it, nt, mt, split);
+        int w_row = nt * kTileN;
+        if (p.tile_expert) {                     // every role skips an unused tile of the plan the same way
+          const int e = p.tile_expert[mt];
+          if (e < 0) continue;
+          w_row += e * p.N;
+        }
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -155,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
           } else {
             mbar_expect_tx(&full[stage], Cfg::kABytes + Cfg::kBBytes);
             tma_load_2d_hint(sA + (size_t) stage * Cfg::kABytes, &tmap_w, &full[stage], kb * Cfg::kKElems,
-                             nt * kTileN, pol_w);
+                             w_row, pol_w);
           }
           tma_load_2d(sB + (size_t) stage * Cfg::kBBytes, &tmap_x, &full[stage], kb * Cfg::kKElems, mt * NT);
           if (++stage == ST) { stage = 0; phase ^= 1; }
@@ -170,6 +178,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
       int stage = 0, phase = 0, acc = 0, acc_phase = 0;
       for (int it = blockIdx.x; it < items; it += gridDim.x) {
         const int split = it % p.splits;
+        if (p.tile_expert) {
+          int nt_, mt_, split_;
+          item_coords(p, it, nt_, mt_, split_);
+          if (p.tile_expert[mt_] < 0) continue;
+        }
         const int kb0 = split * p.kb_per_split;
         const int kb1 = min(kb0 + p.kb_per_split, p.kb_total);
         mbar_wait(&tempty[acc], acc_phase ^ 1);
@@ -201,6 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
     for (int it = blockIdx.x; it < items; it += gridDim.x) {
       int nt, mt, split;
       item_coords(p, it, nt, mt, split);
+      if (p.tile_expert && p.tile_expert[mt] < 0) continue;
       const int n = nt * kTileN + q * 32 + lane;
       const int m0 = mt * NT;
       mbar_wait(&tfull[acc], acc_phase);
@@ -420,7 +434,7 @@ static int launch_gemm_tc(GemmTcParams p, const void* x, const void* w, void* wo
   int rc;
   if constexpr (KIND == kGF16) {
     const CUtensorMapDataType dt16 = p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    rc = make_tmap(&tw, w, dt16, 2, p.N, p.K, kTileN, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = make_tmap(&tw, w, dt16, 2, p.tile_expert ? (int64_t) p.experts * p.N : p.N, p.K, kTileN, 64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap(&tx, x, dt16, 2, p.M, p.K, NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   } else if constexpr (KIND == kGI8) {
@@ -624,6 +638,25 @@ extern "C" int tb_gemm_tc_bf16(void* c, int out_type, const void* x, const void*
   p.c = c; p.out_type = out_type; p.bf16 = 1; p.bias = bias; p.act = act;
   p.M = M; p.N = N; p.K = K;
   return dispatch_nt<kGF16>(p, x, w, workspace, workspace_bytes, counters, 0, 0, stream);
+}
+
+// Routed experts on the same kernel: x bf16 [max_tiles * 128, K] holds the (token, choice) pairs in the order of a plan whose
+// tiles are 128 rows (tb_moe_plan), w bf16 [experts, N, K]; m-tile t multiplies the weights of expert tile_expert[t] (< 0: the
+// tile is skipped by producer, MMA issuer and epilogue alike); c [max_tiles * 128, N] fp32 (out_type 1) or bf16 (3) in the
+// same row order.  A weight tile that runs past an expert's last row reads the next expert's rows; those columns are not stored.
+extern "C" int tb_gemm_tc_bf16_grouped(void* c, int out_type, const void* x, const void* w, const int* tile_expert, int max_tiles,
+                                       int experts, int act, int N, int K, cudaStream_t stream) {
+  using namespace tb;
+  if (!c || !x || !w || !tile_expert || max_tiles < 0 || experts < 1 || N < 1 || K < 8 || K % 8 || (out_type != 1 && out_type != 3) ||
+      (act != 0 && act != 1 && act != 3))
+    return -1;
+  if ((uintptr_t) x % 16 || (uintptr_t) w % 16) return -1;
+  if (max_tiles == 0) return 0;
+  GemmTcParams p{};
+  p.c = c; p.out_type = out_type; p.bf16 = 1; p.act = act;
+  p.M = max_tiles * 128; p.N = N; p.K = K;
+  p.tile_expert = tile_expert; p.experts = experts;
+  return launch_gemm_tc<kGF16, 128>(p, x, w, nullptr, 0, nullptr, 1, stream);
 }
 
 // Gate / up projection with SwiGLU in the tcgen05 epilogue (prefill shapes): w holds [N = 2 * inter, K] (gate rows, then up

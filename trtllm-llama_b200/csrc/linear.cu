@@ -124,6 +124,33 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
+// Few output columns (a router's logits): one warp per output element, lanes stride over k, fp32 multiply-add, partial
+// sums added in a fixed tree — the tile kernel above would leave all but a handful of SMs idle on such a shape.
+template <typename AT, typename WT, typename CT>
+__global__ void __launch_bounds__(256) linear_dot_kernel(LinArgs p) {
+  const int64_t o = blockIdx.x * (int64_t) 8 + threadIdx.x / 32;
+  if (o >= (int64_t) p.M * p.N) return;
+  const int m = (int) (o / p.N), n = (int) (o % p.N), lane = threadIdx.x % 32;
+  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) m * p.lda;
+  const WT* W = reinterpret_cast<const WT*>(p.w) + (int64_t) n * p.K;
+  float acc = 0.f;
+  for (int k = lane; k < p.K; k += 32) acc = fmaf(to_f<AT>(A[k]), to_f<WT>(W[k]), acc);
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    if (p.bias) acc += to_f<WT>(reinterpret_cast<const WT*>(p.bias)[n]);
+    reinterpret_cast<CT*>(p.c)[(int64_t) m * p.ldc + n] = from_f<CT>(apply_act(acc, p.act));
+  }
+}
+
+template <typename AT, typename WT>
+int launch_dot(const LinArgs& p, int c_dtype, cudaStream_t s) {
+  const unsigned grid = (unsigned) (((int64_t) p.M * p.N + 7) / 8);
+  if (c_dtype == TB_DT_F32) linear_dot_kernel<AT, WT, float><<<grid, 256, 0, s>>>(p);
+  else linear_dot_kernel<AT, WT, __nv_bfloat16><<<grid, 256, 0, s>>>(p);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -244,8 +271,12 @@ template <typename AT, typename CT, int MR>
 __global__ void __launch_bounds__(256) linear_gemv_kernel(LinArgs p, int vec_a) {
   extern __shared__ __align__(16) __nv_bfloat16 a_s[];          // [MR][K]
   const int b = blockIdx.y;
-  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) b * p.a_bs;
-  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) b * p.w_bs;
+  // routed experts, few pairs (tb_moe_gemv): batch element b is pair b — its token's row (b / a_div) against the weights
+  // of expert tile_expert[b]
+  const int ab = p.tile_expert && p.a_div > 0 ? b / p.a_div : b;
+  const int wb = p.tile_expert ? p.tile_expert[b] : b;
+  const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) ab * p.a_bs;
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.w) + (int64_t) wb * p.w_bs;
   CT* C = reinterpret_cast<CT*>(p.c) + (int64_t) b * p.c_bs;
   const int K = p.K;
   if (vec_a) {
@@ -425,6 +456,14 @@ extern "C" int tb_linear(void* c, int c_dtype, int64_t ldc, int64_t c_bs, const 
       if (c_dtype == TB_DT_F32) linear_mma_kernel<__nv_bfloat16, float><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
       else linear_mma_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, s>>>(p, vec_a, vec_w);
     }
+  } else if (batch == 1 && N <= 64) {
+    if (w_dtype == TB_DT_BF16) {
+      if (a_dtype == TB_DT_F32) launch_dot<float, __nv_bfloat16>(p, c_dtype, s);
+      else launch_dot<__nv_bfloat16, __nv_bfloat16>(p, c_dtype, s);
+    } else {
+      if (a_dtype == TB_DT_F32) launch_dot<float, float>(p, c_dtype, s);
+      else launch_dot<__nv_bfloat16, float>(p, c_dtype, s);
+    }
   } else if (w_dtype == TB_DT_BF16) {
     if (a_dtype == TB_DT_F32) launch_fma<float, __nv_bfloat16>(p, c_dtype, grid, s);
     else launch_fma<__nv_bfloat16, __nv_bfloat16>(p, c_dtype, grid, s);
@@ -492,6 +531,33 @@ extern "C" int tb_moe_linear(void* c, int c_dtype, int64_t ldc, const void* a, i
     if (a_dtype == TB_DT_F32) launch_fma<float, float>(p, c_dtype, grid, s);
     else launch_fma<__nv_bfloat16, float>(p, c_dtype, grid, s);
   }
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Expert products for a handful of (token, choice) pairs (generation steps): pair b is one single-row product of the
+// streaming kernel against expert ids[b]'s weights, so only the chosen experts' weights are read and no plan is needed.
+// a_div > 0: a [tokens, K], pair b reads row b / a_div; a_div == 0: a [pairs, K].  c [pairs, N] in pair order.
+// act TB_ACT_GATED: w holds per expert N gate rows, then N up rows; c = g * sigmoid(alpha g) * (u + up_shift), no clamp.
+// Returns -3 when the shape is not one the streaming kernel takes.
+extern "C" int tb_moe_gemv(void* c, int c_dtype, int64_t ldc, const void* a, int a_dtype, int64_t lda, const void* w, int w_dtype,
+                           const int* ids, int pairs, int a_div, int N, int K, int act, float alpha, float up_shift,
+                           tb_stream_t stream) {
+  using namespace tb;
+  auto ok = [](int d) { return d == TB_DT_F32 || d == TB_DT_BF16; };
+  if (!c || !a || !w || !ids || !ok(c_dtype) || !ok(a_dtype) || N <= 0 || K <= 0 || pairs < 0 || a_div < 0) return -1;
+  if (pairs == 0) return 0;
+  const int asz = a_dtype == TB_DT_F32 ? 4 : 2;
+  if (w_dtype != TB_DT_BF16 || pairs > 65535 || K % 8 || (uintptr_t) w % 16 || (size_t) K * 2 > 200 * 1024 || (lda * asz) % 16 ||
+      (uintptr_t) a % 16)
+    return -3;
+  const int64_t w_bs = (int64_t) (act == TB_ACT_GATED ? 2 : 1) * N * K;
+  LinArgs p{c, a, w, nullptr, ldc, ldc, lda, lda, w_bs, 0, 1, N, K, act, alpha, 0.f, up_shift, ids, nullptr, a_div, 0};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc;
+  if (a_dtype == TB_DT_F32) rc = c_dtype == TB_DT_F32 ? launch_gemv<float, float>(p, pairs, s) : launch_gemv<float, __nv_bfloat16>(p, pairs, s);
+  else rc = c_dtype == TB_DT_F32 ? launch_gemv<__nv_bfloat16, float>(p, pairs, s) : launch_gemv<__nv_bfloat16, __nv_bfloat16>(p, pairs, s);
+  if (rc) return rc;
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -9,7 +9,8 @@
 //   moe_plan_kernel     one CTA: pairs counted per expert, every expert's range padded to whole tiles of `tile` rows
 //                       (so a tile never mixes experts), tile -> expert table, and sorted slot -> pair index (-1 in the
 //                       padding).  Everything stays on the device: a replayed step graph re-plans with the same launch.
-//   moe_combine_kernel  out[n] = sum_k weight[n, k] * y[n * top + k], k in index order.
+//   moe_gather_rows     the pairs' token rows in plan order as contiguous bf16 (the tcgen05 kernel's TMA operand).
+//   moe_combine_kernel  out[n] = sum_k weight[n, k] * y[row of pair n * top + k], k in index order.
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -100,8 +101,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(int* ids, f
 }
 
 // one CTA of 1024 threads; shared: count [E] | cursor [E]
-__global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* tile_expert, const int* ids, int pairs, int E,
-                                                        int tile, int max_tiles) {
+__global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* tile_expert, int* pair_slot, const int* ids, int pairs,
+                                                        int E, int tile, int max_tiles) {
   extern __shared__ int sm_i[];
   int* count = sm_i;
   int* cursor = sm_i + E;
@@ -131,17 +132,42 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(int* slot_pair, int* til
     if (e >= 0 && e < E) {
       const int s = atomicAdd(&cursor[e], 1);
       if (s < max_tiles * tile) slot_pair[s] = p;
+      if (pair_slot) pair_slot[p] = s < max_tiles * tile ? s : -1;
+    } else if (pair_slot) {
+      pair_slot[p] = -1;
     }
   }
 }
 
-__global__ void moe_combine_kernel(float* out, const float* y, const float* weights, int64_t n, int width, int top) {
+__global__ void moe_combine_kernel(float* out, const float* y, const float* weights, const int* pair_slot, int64_t n, int width,
+                                   int top) {
   for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
     const int64_t row = i / width;
     const int c = (int) (i % width);
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weights[row * top + k], y[(row * top + k) * width + c], acc);
+    for (int k = 0; k < top; ++k) {
+      const int64_t r = pair_slot ? pair_slot[row * top + k] : row * top + k;
+      if (r >= 0) acc = fmaf(weights[row * top + k], y[r * width + c], acc);
+    }
     out[i] = acc;
+  }
+}
+
+// xs[s, :] = bf16(x[slot_pair[s] / top, :]) (zeros in the padding): the pairs' token rows in plan order, as the contiguous
+// operand the tcgen05 kernel loads by TMA
+template <typename T>
+__global__ void moe_gather_rows_kernel(__nv_bfloat16* xs, const T* x, int64_t ldx, const int* slot_pair, int top, int cols) {
+  const int s = blockIdx.x;
+  const int pair = slot_pair[s];
+  __nv_bfloat16* dst = xs + (int64_t) s * cols;
+  if (pair < 0) {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const T* src = x + (int64_t) (pair / top) * ldx;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    if constexpr (sizeof(T) == 4) dst[c] = __float2bfloat16_rn(src[c]);
+    else dst[c] = src[c];
   }
 }
 
@@ -171,25 +197,38 @@ extern "C" int tb_moe_plan_tiles(int pairs, int experts, int tile) {
   return full + (experts < pairs ? experts : pairs);      // every expert in use may end in one partly filled tile
 }
 
-extern "C" int tb_moe_plan(int* slot_pair, int* tile_expert, const int* ids, int pairs, int experts, int tile, int max_tiles,
-                           tb_stream_t stream) {
+extern "C" int tb_moe_plan(int* slot_pair, int* tile_expert, int* pair_slot, const int* ids, int pairs, int experts, int tile,
+                           int max_tiles, tb_stream_t stream) {
   if (!slot_pair || !tile_expert || !ids || pairs < 0 || experts <= 0 || tile <= 0 || max_tiles < tb_moe_plan_tiles(pairs, experts, tile))
     return -1;
   if ((size_t) experts * 2 * sizeof(int) > 48 * 1024) return -2;
   if (pairs == 0) return 0;
-  moe_plan_kernel<<<1, 1024, (size_t) experts * 2 * sizeof(int), (cudaStream_t) stream>>>(slot_pair, tile_expert, ids, pairs,
-                                                                                         experts, tile, max_tiles);
+  moe_plan_kernel<<<1, 1024, (size_t) experts * 2 * sizeof(int), (cudaStream_t) stream>>>(slot_pair, tile_expert, pair_slot, ids,
+                                                                                         pairs, experts, tile, max_tiles);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-extern "C" int tb_moe_combine(float* out, const float* y, const float* weights, int rows, int width, int top,
+extern "C" int tb_moe_gather_rows(void* xs, const void* x, int x_dtype, int64_t ldx, const int* slot_pair, int slots, int top,
+                                  int cols, tb_stream_t stream) {
+  if (!xs || !x || !slot_pair || slots < 0 || top <= 0 || cols <= 0 || (x_dtype != TB_DT_F32 && x_dtype != TB_DT_BF16)) return -1;
+  if (slots == 0) return 0;
+  if (x_dtype == TB_DT_F32)
+    moe_gather_rows_kernel<float><<<slots, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) xs, (const float*) x, ldx, slot_pair, top, cols);
+  else
+    moe_gather_rows_kernel<__nv_bfloat16><<<slots, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) xs, (const __nv_bfloat16*) x, ldx,
+                                                                                    slot_pair, top, cols);
+  TB_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int tb_moe_combine(float* out, const float* y, const float* weights, const int* pair_slot, int rows, int width, int top,
                               tb_stream_t stream) {
   if (!out || !y || !weights || rows < 0 || width <= 0 || top <= 0) return -1;
   if (rows == 0) return 0;
   const int64_t n = (int64_t) rows * width;
   const int grid = (int) ((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, y, weights, n, width, top);
+  moe_combine_kernel<<<grid, 256, 0, (cudaStream_t) stream>>>(out, y, weights, pair_slot, n, width, top);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -5,7 +5,7 @@
 // Pool entry of one position: [G][dim] rotated keys, then [G][vdim] values (G key/value heads).  Query head h reads
 // key/value head h / (H / G).
 //
-//   qkv_conv_rope_append_kernel   one thread per (row, channel) of the concatenated q | k | v projection: the causal
+//   qkv_conv_rope_append_kernel   one thread per (row, channel; rows along grid x) of the concatenated q | k | v projection: the causal
 //                                 convolution over the row's own portion and the sequence's carried inputs, the
 //                                 rotation of the head's leading `dims` elements (interleaved pairs; the partner's
 //                                 convolution is recomputed), and the store: queries to their buffer, keys and values
@@ -67,9 +67,8 @@ __device__ __forceinline__ float conv_at(const QkvArgs& a, const float* st, int 
 template <typename T>
 __global__ void qkv_conv_rope_append_kernel(T* q_out, T* pool, QkvArgs a) {
   const int Cq = a.H * a.dim, Ck = a.G * a.dim, Cv = a.G * a.vdim, C = Cq + Ck + Cv;
-  const int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x;
-  if (i >= (int64_t) a.rows * C) return;
-  const int row = (int) (i / C), ch = (int) (i % C);
+  const int row = blockIdx.x, ch = blockIdx.y * blockDim.x + threadIdx.x;
+  if (ch >= C) return;
   const int e = a.tok_seq[row], pos = a.tok_pos[row], past = a.seq_past[e], start = a.seq_start[e];
   const float* st = a.state + (int64_t) a.seq_slot[e] * (a.taps - 1) * C;
   float y = conv_at(a, st, C, ch, pos, past, start);
@@ -436,8 +435,9 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
   if (rows == 0) return 0;
   QkvArgs a{proj, ldp, conv_w, w_dtype, state, table, tok_seq, tok_pos, seq_start, seq_past, seq_slot, block_table,
             max_blocks, page, rows, heads, kv_heads, dim, vdim, dims, taps};
-  const int64_t n = (int64_t) rows * ((int64_t) heads * dim + (int64_t) kv_heads * (dim + vdim));
-  const unsigned grid = (unsigned) ((n + 255) / 256);
+  const int C = heads * dim + kv_heads * (dim + vdim);
+  if ((C + 255) / 256 > 65535) return -2;
+  const dim3 grid(rows, (C + 255) / 256);
   if (dtype == TB_DT_F32) qkv_conv_rope_append_kernel<float><<<grid, 256, 0, (cudaStream_t) stream>>>((float*) q_out, (float*) pool, a);
   else qkv_conv_rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) q_out, (__nv_bfloat16*) pool, a);
   TB_CHECK_CUDA(cudaGetLastError());

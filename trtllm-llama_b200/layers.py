@@ -180,8 +180,9 @@ class RoutedExpertsMLP:
     Router (fp32): s = sigmoid(W_router h); choice = s + correction; the experts form ``groups`` equal groups of
     neighbours, a group scores the sum of its two largest choices and only the ``keep`` best groups stay eligible; the
     ``top`` largest eligible choices are taken and weighted by their plain s (not renormalised).  The (token, choice)
-    pairs are sorted by expert on the device into whole tiles and both expert products walk that plan, so a step costs
-    ``top`` experts per token whatever the batch."""
+    pairs are sorted by expert on the device into whole tiles and both expert products walk that plan (tcgen05 tiles of
+    128 rows for bf16, warp-MMA / FMA tiles of 64 otherwise), so a step costs ``top`` experts per token whatever the
+    batch; a generation step's few pairs run one streaming product each instead."""
 
     def __init__(self, *, w_router, correction, w_gate, w_up, w_down, top, groups=1, keep=1):
         """w_gate, w_up: [experts, ff, width]; w_down: [experts, width, ff]."""
@@ -193,14 +194,28 @@ class RoutedExpertsMLP:
         self.w_down, self.dtype = w_down.contiguous(), w_down.dtype
 
     def forward(self, x, ctx):
-        n = x.shape[0]
+        n, top, K = x.shape[0], self.top, x.shape[1]
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32, compute=ops.COMPUTE_FMA32)
-        ids, weights = ops.moe_route(logits, self.correction, self.top, self.groups, self.keep)
-        slot_pair, tile_expert = ops.moe_plan(ids, self.experts)
-        gu = ops.moe_linear(x, self.w_gate_up, slot_pair, tile_expert, a_div=self.top, c_rows=0, out_dtype=torch.float32)
-        act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)                  # silu(gate) * up
-        y = ops.moe_linear(act, self.w_down, slot_pair, tile_expert, a_div=0, c_rows=n * self.top, out_dtype=torch.float32)
-        return ops.moe_combine(y, weights)
+        ids, weights = ops.moe_route(logits, self.correction, top, self.groups, self.keep)
+        bf16 = self.dtype == torch.bfloat16
+        if bf16 and n * top <= ops.MOE_GEMV_MAX_PAIRS and not ops.FORCE_TILE_LINEAR:
+            # generation steps: one streaming product per pair, gate / up and the activation in one kernel, no plan
+            act = ops.moe_gemv(x, self.w_gate_up, ids, a_div=top, out_dtype=self.dtype, gated=True)
+            y = ops.moe_gemv(act, self.w_down, ids, a_div=0, out_dtype=torch.float32) if act is not None else None
+            if y is not None:
+                return ops.moe_combine(y, weights)
+        if bf16 and n * top >= ops.TC_MIN_ROWS and K % 8 == 0 and self.w_down.shape[2] % 8 == 0 and not ops.FORCE_TILE_LINEAR:
+            # prompt-sized steps: the tcgen05 kernel over a plan of 128-row tiles
+            slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE_TC)
+            gu = ops.moe_linear_tc(ops.moe_gather_rows(x, slot_pair, top), self.w_gate_up, tile_expert, torch.float32)
+            act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)              # silu(gate) * up
+            y = ops.moe_linear_tc(act, self.w_down, tile_expert, torch.float32)
+            return ops.moe_combine(y, weights, pair_slot)
+        slot_pair, tile_expert, pair_slot = ops.moe_plan(ids, self.experts, ops.MOE_TILE)
+        gu = ops.moe_linear(x, self.w_gate_up, slot_pair, tile_expert, a_div=top, out_dtype=torch.float32)
+        act = ops.gated_act(gu, self.dtype, 1.0, 0.0, 0.0)
+        y = ops.moe_linear(act, self.w_down, slot_pair, tile_expert, a_div=0, out_dtype=torch.float32)
+        return ops.moe_combine(y, weights, pair_slot)
 
 
 class ClampedGatedMLP:

@@ -103,7 +103,8 @@ class OpTimer:
 
     NAMES = ("linear", "linear_gated", "embed_scaled", "rmsnorm_rows", "gated_act", "rope_table", "rope_query_tail", "latent_kv_append",
              "latent_attention", "causal_conv1d", "rglru_scan", "qkv_conv_rope_append", "window_attention", "moe_route",
-             "moe_plan", "moe_linear", "moe_combine", "add_row_vector", "tanh_cap")
+             "moe_plan", "moe_linear", "moe_linear_tc", "moe_gemv", "moe_gather_rows", "moe_combine", "add_row_vector", "tanh_cap",
+             "residual_norm_rows")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.rec, self.saved = torch, ops, [], {}
@@ -154,14 +155,17 @@ class OpTimer:
             proj, H, G, d, dv = args[0], args[8], args[9], args[10], args[11]
             C = H * d + G * (d + dv)
             return name, 0.0, proj.shape[0] * C * (4 + args[5].element_size())
-        if name == "moe_linear":
-            a, w, slot_pair = args[0], args[1], args[2]
-            pairs = (kw.get("c_rows") or 0) or (a.shape[0] * kw["a_div"] if kw.get("a_div") else 0)
-            self._pairs = pairs or getattr(self, "_pairs", slot_pair.numel())
+        if name == "moe_route":
+            self._pairs = args[0].shape[0] * args[2]            # rows * top: the pairs the expert products below work on
+            return name, 0.0, nb(args[0], *out)
+        if name in ("moe_linear", "moe_linear_tc", "moe_gemv"):
+            a, w = args[0], args[1]
+            if out is None:
+                return name + " (not taken)", 0.0, 0
             E, N, K = w.shape
             used = min(E, self._pairs)
-            return f"moe_linear {self._pairs}x{N}x{K} of {E}", 2.0 * self._pairs * N * K, \
-                used * N * K * w.element_size() + self._pairs * (K * a.element_size() + N * out.element_size())
+            return f"{name} {self._pairs}x{N}x{K} of {E}", 2.0 * self._pairs * N * K, \
+                used * N * K * w.element_size() + self._pairs * (K * a.element_size() + out.shape[1] * out.element_size())
         if name == "latent_kv_append":
             pool, kv, lat, rot = args[0], args[1], args[8], args[9]
             return name, 0.0, kv.shape[0] * (lat + rot) * (4 + pool.element_size())

@@ -608,7 +608,9 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
     return out
 
 
-MOE_TILE = 64
+MOE_TILE = 64            # tile height of the warp-MMA / FMA expert products
+MOE_TILE_TC = 128        # ... of the tcgen05 expert products
+MOE_GEMV_MAX_PAIRS = 64  # up to this many (token, choice) pairs a step runs the streaming kernel per pair, without a plan
 
 
 def moe_route(logits, correction, top, groups, keep):
@@ -623,38 +625,78 @@ def moe_route(logits, correction, top, groups, keep):
     return ids, weights
 
 
-def moe_plan(ids, experts):
-    """-> (slot_pair int32 [tiles * MOE_TILE], tile_expert int32 [tiles]): the pairs sorted by expert in whole tiles."""
+def moe_plan(ids, experts, tile=MOE_TILE):
+    """-> (slot_pair int32 [tiles * tile], tile_expert int32 [tiles], pair_slot int32 [pairs]): the pairs sorted by expert
+    in whole tiles, and where each pair went."""
     _chk_cuda(ids)
     pairs = ids.numel()
-    tiles = _rl.tb_moe_plan_tiles(pairs, experts, MOE_TILE)
-    slot_pair = torch.empty((tiles * MOE_TILE,), dtype=torch.int32, device=ids.device)
+    tiles = _rl.tb_moe_plan_tiles(pairs, experts, tile)
+    slot_pair = torch.empty((tiles * tile,), dtype=torch.int32, device=ids.device)
     tile_expert = torch.empty((tiles,), dtype=torch.int32, device=ids.device)
-    check(_rl.tb_moe_plan(_p(slot_pair), _p(tile_expert), _p(ids), pairs, experts, MOE_TILE, tiles, _stream()), "tb_moe_plan")
-    return slot_pair, tile_expert
+    pair_slot = torch.empty((pairs,), dtype=torch.int32, device=ids.device)
+    check(_rl.tb_moe_plan(_p(slot_pair), _p(tile_expert), _p(pair_slot), _p(ids), pairs, experts, tile, tiles, _stream()),
+          "tb_moe_plan")
+    return slot_pair, tile_expert, pair_slot
 
 
-def moe_linear(a, w, slot_pair, tile_expert, *, a_div, c_rows, out_dtype, act=ACT_NONE, compute=COMPUTE_AUTO):
-    """Expert products over a plan.  w [experts, N, K].  a_div > 0: ``a`` holds token rows and slot s reads row
-    slot_pair[s] // a_div; a_div == 0: ``a`` holds one row per slot.  c_rows == 0: the result has one row per slot;
-    c_rows > 0: that many rows, row = the pair's index."""
+def moe_linear(a, w, slot_pair, tile_expert, *, a_div, out_dtype, act=ACT_NONE, compute=COMPUTE_AUTO):
+    """Expert products over a plan with tiles of MOE_TILE rows (warp-MMA tiles for bf16 weights, fp32 FMA tiles otherwise).
+    w [experts, N, K].  a_div > 0: ``a`` holds token rows and slot s reads row slot_pair[s] // a_div; a_div == 0: ``a``
+    holds one row per slot.  The result has one row per slot."""
     _chk_dev(a, w, slot_pair, tile_expert)
     _, N, K = w.shape
     if not w.is_contiguous() or a.stride(1) != 1 or a.shape[1] != K:
         raise ValueError("moe_linear: w [experts, N, K] contiguous, a [*, K]")
-    out = torch.empty((c_rows or slot_pair.numel(), N), dtype=out_dtype, device=a.device)
+    out = torch.empty((slot_pair.numel(), N), dtype=out_dtype, device=a.device)
     check(_rl.tb_moe_linear(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w), _dt(w), _p(slot_pair),
-                            _p(tile_expert), tile_expert.numel(), int(a_div), int(c_rows > 0), N, K, act, compute, _stream()),
+                            _p(tile_expert), tile_expert.numel(), int(a_div), 0, N, K, act, compute, _stream()),
           "tb_moe_linear")
     return out
 
 
-def moe_combine(y, weights):
-    """out[n] = sum_k weights[n, k] * y[n * top + k]  (fp32)."""
-    _chk_cuda(y, weights)
+def moe_gather_rows(x, slot_pair, top):
+    """bf16 [slots, K]: the pairs' token rows in plan order (zeros in the padding)."""
+    _chk_dev(x, slot_pair)
+    out = torch.empty((slot_pair.numel(), x.shape[1]), dtype=torch.bfloat16, device=x.device)
+    check(_rl.tb_moe_gather_rows(_p(out), _p(x), _dt(x), x.stride(0), _p(slot_pair), slot_pair.numel(), top, x.shape[1],
+                                 _stream()), "tb_moe_gather_rows")
+    return out
+
+
+def moe_linear_tc(xs, w, tile_expert, out_dtype, act=ACT_NONE):
+    """Expert products on the tcgen05 kernel over a plan with tiles of MOE_TILE_TC rows: xs bf16 [slots, K] contiguous in
+    plan order, w bf16 [experts, N, K]; one result row per slot."""
+    _chk_cuda(xs, w, tile_expert)
+    E, N, K = w.shape
+    out = torch.empty((xs.shape[0], N), dtype=out_dtype, device=xs.device)
+    check(_rl.tb_gemm_tc_bf16_grouped(_p(out), 1 if out_dtype == torch.float32 else 3, _p(xs), _p(w), _p(tile_expert),
+                                      tile_expert.numel(), E, act, N, K, _stream()), "tb_gemm_tc_bf16_grouped")
+    return out
+
+
+def moe_gemv(a, w, ids, *, a_div, out_dtype, gated=False):
+    """Expert products for few pairs without a plan: pair b against expert ids[b].  gated: w [experts, 2 N, K] and the
+    result is silu(gate) * up.  Returns None when the streaming kernel does not take the shape."""
+    _chk_dev(a, w, ids)
+    E, rows_w, K = w.shape
+    N = rows_w // 2 if gated else rows_w
+    pairs = ids.numel()
+    out = torch.empty((pairs, N), dtype=out_dtype, device=a.device)
+    rc = _rl.tb_moe_gemv(_p(out), _dt(out), out.stride(0), _p(a), _dt(a), a.stride(0), _p(w), _dt(w), _p(ids), pairs, int(a_div),
+                         N, K, 2 if gated else ACT_NONE, 1.0, 0.0, _stream())
+    if rc == -3:
+        return None
+    check(rc, "tb_moe_gemv")
+    return out
+
+
+def moe_combine(y, weights, pair_slot=None):
+    """out[n] = sum_k weights[n, k] * y[row of pair n * top + k]  (fp32); the pair's row is pair_slot[pair], or the pair's
+    index when ``y`` is in pair order."""
+    _chk_cuda(y, weights, pair_slot)
     rows, top = weights.shape
     out = torch.empty((rows, y.shape[1]), dtype=torch.float32, device=y.device)
-    check(_rl.tb_moe_combine(_p(out), _p(y), _p(weights), rows, y.shape[1], top, _stream()), "tb_moe_combine")
+    check(_rl.tb_moe_combine(_p(out), _p(y), _p(weights), _p(pair_slot), rows, y.shape[1], top, _stream()), "tb_moe_combine")
     return out
 
 
