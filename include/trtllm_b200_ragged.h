@@ -167,13 +167,16 @@ int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* pro
  * result does not depend on how its prompt was cut or on the batch around it.  vdim <= 256.
  * bf16 with a (dim, vdim) pair the tensor-core kernel is built for (tb_window_attention_tensor_cores tells) runs on
  * tensor cores when the per-sequence description is given: seq_start / seq_len / seq_past [seqs] and max_len >= the longest
- * seq_len (host; it sizes the grid).  mode 1 keeps any configuration on the SIMT kernel (A/B). */
+ * seq_len (host; it sizes the grid).  nsplit > 1 (tensor-core form only) deals every row block's key tiles to nsplit CTAs
+ * whose partial results (workspace: fp32 [rows, heads, nsplit, vdim + 2]) a second kernel merges in index order — for steps
+ * with few rows (generation), so that more than a handful of SMs read the cache.  mode 1 keeps any configuration on the
+ * SIMT kernel (A/B). */
 int tb_window_attention_tensor_cores(int dtype, int heads, int kv_heads, int dim, int vdim);
 int tb_window_attention(void* out, const void* q, const void* pool, int dtype, const float* gate, int64_t ldg,
                         const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos, const int* block_table,
                         const int* seq_start, const int* seq_len, const int* seq_past, int seqs, int max_len,
                         int max_blocks, int page, int rows, int heads, int kv_heads, int dim, int vdim, float scale,
-                        int window, int mode, tb_stream_t stream);
+                        int window, int mode, int nsplit, float* workspace, tb_stream_t stream);
 
 /* ---- routed-expert feed-forward ------------------------------------------------------------------------------------
  * tb_moe_route: logits fp32 [N, experts].  s = sigmoid(logit); choice = s + correction (fp32 or bf16 [experts], NULL:

@@ -204,7 +204,7 @@ RAGGED_SIGNATURES = {
                                       i32, i32, i32, i32, vp]),
     "tb_window_attention_tensor_cores": (i32, [i32, i32, i32, i32, i32]),
     "tb_window_attention": (i32, [vp, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
-                                  i32, i32, f32, i32, i32, vp]),
+                                  i32, i32, f32, i32, i32, i32, vp, vp]),
     "tb_moe_route": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "tb_moe_plan_tiles": (i32, [i32, i32, i32]),
     "tb_moe_plan": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, vp]),

@@ -64,27 +64,37 @@ __device__ __forceinline__ float conv_at(const QkvArgs& a, const float* st, int 
   return acc;
 }
 
+// one thread per (row, pair of neighbouring channels): both convolutions once, the rotation, one 2-element store
 template <typename T>
 __global__ void qkv_conv_rope_append_kernel(T* q_out, T* pool, QkvArgs a) {
   const int Cq = a.H * a.dim, Ck = a.G * a.dim, Cv = a.G * a.vdim, C = Cq + Ck + Cv;
-  const int row = blockIdx.x, ch = blockIdx.y * blockDim.x + threadIdx.x;
+  const int row = blockIdx.x, ch = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
   if (ch >= C) return;
   const int e = a.tok_seq[row], pos = a.tok_pos[row], past = a.seq_past[e], start = a.seq_start[e];
   const float* st = a.state + (int64_t) a.seq_slot[e] * (a.taps - 1) * C;
-  float y = conv_at(a, st, C, ch, pos, past, start);
+  const bool two = ch + 1 < C;
+  float y0 = conv_at(a, st, C, ch, pos, past, start), y1 = two ? conv_at(a, st, C, ch + 1, pos, past, start) : 0.f;
   if (ch < Cq + Ck) {
-    const int d = (ch < Cq ? ch : ch - Cq) % a.dim;
+    const int d = (ch < Cq ? ch : ch - Cq) % a.dim;      // even: a.dim is even whenever anything is rotated
     if (d < a.dims) {
-      const float yp = conv_at(a, st, C, ch ^ 1, pos, past, start);      // dim-aligned pairs: heads start at even channels
       const float* cs = a.table + ((int64_t) row * (a.dims / 2) + d / 2) * 2;
-      y = (d & 1) ? fmaf(y, cs[0], yp * cs[1]) : fmaf(y, cs[0], -yp * cs[1]);
+      const float u = y0, v = y1;
+      y0 = fmaf(u, cs[0], -v * cs[1]);
+      y1 = fmaf(v, cs[0], u * cs[1]);
     }
   }
-  if (ch < Cq) {
-    q_out[(int64_t) row * Cq + ch] = from_f<T>(y);
-  } else {
-    const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
-    pool[slot * (Ck + Cv) + (ch - Cq)] = from_f<T>(y);
+  // q | k | v boundaries may be odd only when nothing is rotated: store the two elements one by one
+  #pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int c = ch + i;
+    if (c >= C) break;
+    const float y = i ? y1 : y0;
+    if (c < Cq) {
+      q_out[(int64_t) row * Cq + c] = from_f<T>(y);
+    } else {
+      const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
+      pool[slot * (Ck + Cv) + (c - Cq)] = from_f<T>(y);
+    }
   }
 }
 
@@ -220,20 +230,26 @@ constexpr int kMmaRows = 64, kMmaKeys = 64;
 struct MmaArgs {
   AttnArgs a;
   const int *seq_start, *seq_len, *seq_past;
+  int nsplit;              // > 1: the key tiles of a row block are dealt round-robin to nsplit CTAs (blockIdx.x = block * nsplit + split)
+  float* partial;          // nsplit > 1: [rows, H, nsplit, VDIM + 2] = m (log2 units), l, unnormalised o — merged by a second kernel
 };
 
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16* out, const __nv_bfloat16* q,
+__global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloat16* out, const __nv_bfloat16* q,
                                                                    const __nv_bfloat16* pool, MmaArgs m) {
   constexpr int LDQ = DIM + 8, LDV = VDIM + 8;        // +16 bytes per row: ldmatrix rows fall into distinct banks
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][LDQ]
-  __nv_bfloat16* ks = qs + kMmaRows * LDQ;                                   // [2][64][LDQ]
-  __nv_bfloat16* vs = ks + 2 * kMmaKeys * LDQ;                               // [2][64][LDV]
+  // K [2][64][LDQ] | V [2][64][LDV]; the query tile [64][LDQ] borrows the K ring's second stage until its fragments sit in
+  // registers (that stage is first filled inside the key loop)
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* vs = ks + 2 * kMmaKeys * LDQ;
+  __nv_bfloat16* qs = ks + kMmaKeys * LDQ;
+  __shared__ int64_t key_row[2][kMmaKeys];            // pool row of every key of a stage (-1: zero-fill)
   const AttnArgs& a = m.a;
   const int e = blockIdx.y, g = blockIdx.z;
   const int per = a.H / a.G, len = m.seq_len[e], past = m.seq_past[e], row0 = m.seq_start[e];
-  const int r0 = blockIdx.x * kMmaRows;                 // first (token, head) row of this CTA
+  const int split = m.nsplit > 1 ? blockIdx.x % m.nsplit : 0, nsplit = m.nsplit > 1 ? m.nsplit : 1;
+  const int r0 = (blockIdx.x / nsplit) * kMmaRows;      // first (token, head) row of this CTA
   if (r0 >= len * per) return;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gq = lane / 4, tq = lane % 4;
   const int t_first = r0 / per;
@@ -252,26 +268,29 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16
     if (t < len) v = *reinterpret_cast<const uint4*>(q + ((int64_t) (row0 + t) * a.H + g * per + hl) * DIM + c);
     *reinterpret_cast<uint4*>(qs + r * LDQ + c) = v;
   }
-  auto load_tile = [&](int kt, int stage) {
-    const int j0 = kt * kMmaKeys;
+  // the page arithmetic runs once per key and tile (64 threads), not once per 16-byte chunk
+  auto locate_tile = [&](int kt, int stage) {
+    if (threadIdx.x < kMmaKeys) {
+      const int j = kt * kMmaKeys + threadIdx.x;
+      key_row[stage][threadIdx.x] = (j >= lo_cta && j <= p_last) ? ((int64_t) bt[j / a.page] * a.page + j % a.page) * E : -1;
+    }
+  };
+  auto load_tile = [&](int stage) {
     __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
     __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
     for (int i = threadIdx.x; i < kMmaKeys * (DIM / 8); i += 128) {
-      const int jj = i / (DIM / 8), c = (i % (DIM / 8)) * 8, j = j0 + jj;
-      const bool ok = j >= lo_cta && j <= p_last;
-      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / a.page] * a.page + j % a.page) * E + g * DIM + c : pool;
-      cp_async16(kd + jj * LDQ + c, src, ok);
+      const int jj = i / (DIM / 8), c = (i % (DIM / 8)) * 8;
+      const int64_t r = key_row[stage][jj];
+      cp_async16(kd + jj * LDQ + c, r >= 0 ? pool + r + g * DIM + c : pool, r >= 0);
     }
     for (int i = threadIdx.x; i < kMmaKeys * (VDIM / 8); i += 128) {
-      const int jj = i / (VDIM / 8), c = (i % (VDIM / 8)) * 8, j = j0 + jj;
-      const bool ok = j >= lo_cta && j <= p_last;
-      const __nv_bfloat16* src = ok ? pool + ((int64_t) bt[j / a.page] * a.page + j % a.page) * E + a.G * DIM + g * VDIM + c : pool;
-      cp_async16(vd + jj * LDV + c, src, ok);
+      const int jj = i / (VDIM / 8), c = (i % (VDIM / 8)) * 8;
+      const int64_t r = key_row[stage][jj];
+      cp_async16(vd + jj * LDV + c, r >= 0 ? pool + r + a.G * DIM + g * VDIM + c : pool, r >= 0);
     }
   };
-  const int kt0 = lo_cta / kMmaKeys, kt1 = p_last / kMmaKeys;
-  load_tile(kt0, 0);
-  cp_async_commit();
+  const int kt0 = lo_cta / kMmaKeys + split, kt1 = p_last / kMmaKeys;
+  locate_tile(kt0, 0);
 
   // the two rows of this thread: warp * 16 + gq and + 8
   int pos_r[2], lo_r[2], head_r[2];
@@ -287,7 +306,8 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16
     m_r[h] = -INFINITY;
     l_r[h] = 0.f;
     // the sink: a term exp(sink - m) of the denominator without a value; one thread of the row's quad carries it
-    if (a.sink && live_r[h]) { m_r[h] = ld_w(a.sink, a.sink_dtype, head_r[h]) * 1.4426950408889634f; l_r[h] = tq == 0 ? 1.f : 0.f; }
+    // (with the keys split over CTAs the merge kernel adds it instead)
+    if (a.sink && live_r[h] && nsplit == 1) { m_r[h] = ld_w(a.sink, a.sink_dtype, head_r[h]) * 1.4426950408889634f; l_r[h] = tq == 0 ? 1.f : 0.f; }
   }
   const float scale2 = a.scale * 1.4426950408889634f;   // scores in units of log 2: exp2f below
   float o[VDIM / 8][4];
@@ -295,18 +315,23 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16
   for (int n = 0; n < VDIM / 8; ++n)
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
-  __syncthreads();                                      // qs is written
+  __syncthreads();                                      // qs and key_row[0] are written
+  if (kt0 <= kt1) load_tile(0);
+  cp_async_commit();
   uint32_t qf[DIM / 16][4];
 #pragma unroll
   for (int kk = 0; kk < DIM / 16; ++kk)
     ldsm_x4(qf[kk], qs + (warp * 16 + lane % 16) * LDQ + kk * 16 + (lane / 16) * 8);
+  if (kt0 + nsplit <= kt1) locate_tile(kt0 + nsplit, 1);
+  __syncthreads();                                      // the query tile's stage may be filled; key_row[1] is written
 
-  for (int kt = kt0; kt <= kt1; ++kt) {
-    const int stage = (kt - kt0) & 1;
-    if (kt < kt1) load_tile(kt + 1, stage ^ 1);         // the other stage was consumed before the barrier that ended kt - 1
+  int stage = 0;
+  for (int kt = kt0; kt <= kt1; kt += nsplit, stage ^= 1) {
+    if (kt + nsplit <= kt1) load_tile(stage ^ 1);       // that stage was consumed before the barrier that ended the last trip
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
+    if (kt + 2 * nsplit <= kt1) locate_tile(kt + 2 * nsplit, stage);   // rows of the tile after next: read by load_tile next trip
     const __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
     const __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
     const int j0 = kt * kMmaKeys;
@@ -378,6 +403,25 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16
     __syncthreads();                                    // this stage may be overwritten by the load issued next trip
   }
   cp_async_wait<0>();
+  if (nsplit > 1) {
+    // unnormalised partial result of this CTA's share of the keys
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float l = l_r[h];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      if (!live_r[h]) continue;
+      const int R = r0 + warp * 16 + gq + h * 8, t = R / per;
+      float* dst = m.partial + (((int64_t) (row0 + t) * a.H + head_r[h]) * nsplit + split) * (VDIM + 2);
+      if (tq == 0) { dst[0] = m_r[h]; dst[1] = l; }
+#pragma unroll
+      for (int n = 0; n < VDIM / 8; ++n) {
+        dst[2 + n * 8 + 2 * tq] = o[n][2 * h];
+        dst[2 + n * 8 + 2 * tq + 1] = o[n][2 * h + 1];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float l = l_r[h];
@@ -398,17 +442,42 @@ __global__ void __launch_bounds__(128) window_attention_mma_kernel(__nv_bfloat16
   }
 }
 
+// one CTA per (row, head): splits merged in index order, the sink added once, gate applied
+__global__ void window_attention_merge_kernel(__nv_bfloat16* out, const float* partial, AttnArgs a, int nsplit, int vdim) {
+  const int row = blockIdx.x, head = blockIdx.y;
+  const float* src = partial + ((int64_t) row * a.H + head) * nsplit * (vdim + 2);
+  const float sink2 = a.sink ? ld_w(a.sink, a.sink_dtype, head) * 1.4426950408889634f : -INFINITY;
+  float M = sink2;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, src[s * (vdim + 2)]);
+  float l = a.sink ? exp2f(sink2 - M) : 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = src[s * (vdim + 2)];
+    if (ms != -INFINITY) l += src[s * (vdim + 2) + 1] * exp2f(ms - M);
+  }
+  float f = 1.f / l;
+  if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) row * a.ldg + head]));
+  for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = src[s * (vdim + 2)];
+      if (ms != -INFINITY) acc = fmaf(src[s * (vdim + 2) + 2 + c], exp2f(ms - M), acc);
+    }
+    out[((int64_t) row * a.H + head) * vdim + c] = __float2bfloat16_rn(acc * f);
+  }
+}
+
 template <int DIM, int VDIM>
 int launch_window_mma(__nv_bfloat16* out, const __nv_bfloat16* q, const __nv_bfloat16* pool, const MmaArgs& m, int seqs,
                       int max_len, cudaStream_t s) {
-  constexpr size_t smem = ((size_t) kMmaRows * (DIM + 8) + 2 * kMmaKeys * (DIM + 8) + 2 * kMmaKeys * (VDIM + 8)) * 2;
+  constexpr size_t smem = ((size_t) 2 * kMmaKeys * (DIM + 8) + 2 * kMmaKeys * (VDIM + 8)) * 2;
   static bool raised = false;
   if (!raised && smem > 48 * 1024) {
     TB_CHECK_CUDA(cudaFuncSetAttribute(window_attention_mma_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
     raised = true;
   }
   const int per = m.a.H / m.a.G;
-  dim3 grid(((int64_t) max_len * per + kMmaRows - 1) / kMmaRows, seqs, m.a.G);
+  const int nsplit = m.nsplit > 1 ? m.nsplit : 1;
+  dim3 grid((((int64_t) max_len * per + kMmaRows - 1) / kMmaRows) * nsplit, seqs, m.a.G);
   window_attention_mma_kernel<DIM, VDIM><<<grid, 128, smem, s>>>(out, q, pool, m);
   return 0;
 }
@@ -436,8 +505,8 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
   QkvArgs a{proj, ldp, conv_w, w_dtype, state, table, tok_seq, tok_pos, seq_start, seq_past, seq_slot, block_table,
             max_blocks, page, rows, heads, kv_heads, dim, vdim, dims, taps};
   const int C = heads * dim + kv_heads * (dim + vdim);
-  if ((C + 255) / 256 > 65535) return -2;
-  const dim3 grid(rows, (C + 255) / 256);
+  if ((C + 511) / 512 > 65535) return -2;
+  const dim3 grid(rows, (C + 511) / 512);
   if (dtype == TB_DT_F32) qkv_conv_rope_append_kernel<float><<<grid, 256, 0, (cudaStream_t) stream>>>((float*) q_out, (float*) pool, a);
   else qkv_conv_rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) q_out, (__nv_bfloat16*) pool, a);
   TB_CHECK_CUDA(cudaGetLastError());
@@ -456,7 +525,8 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
                                    const void* sink, int sink_dtype, const int* tok_seq, const int* tok_pos,
                                    const int* block_table, const int* seq_start, const int* seq_len, const int* seq_past,
                                    int seqs, int max_len, int max_blocks, int page, int rows, int heads, int kv_heads,
-                                   int dim, int vdim, float scale, int window, int mode, tb_stream_t stream) {
+                                   int dim, int vdim, float scale, int window, int mode, int nsplit, float* workspace,
+                                   tb_stream_t stream) {
   if (!out || !q || !pool || !tok_seq || !tok_pos || !block_table) return -1;
   if (dtype != TB_DT_F32 && dtype != TB_DT_BF16) return -1;
   if (sink && sink_dtype != TB_DT_F32 && sink_dtype != TB_DT_BF16) return -1;
@@ -469,7 +539,8 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
   cudaStream_t s = (cudaStream_t) stream;
   if (mode == 0 && seq_start && seq_len && seq_past && seqs > 0 && max_len > 0 && seqs <= 65535 &&
       tb_window_attention_tensor_cores(dtype, heads, kv_heads, dim, vdim) && (uintptr_t) q % 16 == 0 && (uintptr_t) pool % 16 == 0) {
-    MmaArgs m{a, seq_start, seq_len, seq_past};
+    if (nsplit > 1 && !workspace) return -1;
+    MmaArgs m{a, seq_start, seq_len, seq_past, nsplit > 1 ? nsplit : 1, workspace};
 #define X(D, V)                                                                                                     \
   if (dim == D && vdim == V) {                                                                                      \
     const int rc = launch_window_mma<D, V>((__nv_bfloat16*) out, (const __nv_bfloat16*) q, (const __nv_bfloat16*) pool, m, \
@@ -479,6 +550,10 @@ extern "C" int tb_window_attention(void* out, const void* q, const void* pool, i
     TB_WINDOW_MMA_SHAPES(X)
 #undef X
     TB_CHECK_CUDA(cudaGetLastError());
+    if (nsplit > 1) {
+      window_attention_merge_kernel<<<dim3(rows, heads), vdim < 128 ? 64 : 128, 0, s>>>((__nv_bfloat16*) out, workspace, a, nsplit, vdim);
+      TB_CHECK_CUDA(cudaGetLastError());
+    }
     return 0;
   }
   const size_t smem = ((size_t) kTile * (dim + 1) + (size_t) kTile * vdim + (size_t) kWarps * dim) * sizeof(float);

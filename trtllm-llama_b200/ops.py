@@ -599,11 +599,19 @@ def window_attention(q, pool, batch, page, kv_heads, vdim, scale, window, sink=N
     out = torch.empty((rows, heads, vdim), dtype=q.dtype, device=q.device)
     if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
         raise ValueError("gate logits are fp32 with unit inner stride")
+    nsplit, ws = 1, None
+    if not FORCE_SIMT_ATTENTION and _rl.tb_window_attention_tensor_cores(_dt(pool), heads, kv_heads, dim, vdim):
+        # few row blocks (generation steps): deal each block's key tiles to several CTAs so that the chip reads the cache
+        ctas = -(-batch.max_len * (heads // kv_heads) // 64) * batch.num_seqs * kv_heads
+        span = min(window, batch.max_pos + 1) if window else batch.max_pos + 1
+        nsplit = max(1, min(32, 296 // ctas, span // 64 + 1))
+        if nsplit > 1:
+            ws = torch.empty((rows * heads * nsplit * (vdim + 2),), dtype=torch.float32, device=q.device)
     check(_rl.tb_window_attention(_p(out), _p(q), _p(pool), _dt(pool), _p(gate), gate.stride(0) if gate is not None else 0,
                                   _p(sink), _dt(sink) if sink is not None else 0, _p(batch.tok_seq), _p(batch.tok_pos),
                                   _p(batch.block_table), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
                                   batch.num_seqs, batch.max_len, batch.max_blocks, page, rows, heads, kv_heads, dim, vdim,
-                                  float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, _stream()),
+                                  float(scale), int(window), 1 if FORCE_SIMT_ATTENTION else 0, nsplit, _p(ws), _stream()),
           "tb_window_attention")
     return out
 
