@@ -124,27 +124,40 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Few output columns (a router's logits): one warp per output element, lanes stride over k, fp32 multiply-add, partial
-// sums added in a fixed tree — the tile kernel above would leave all but a handful of SMs idle on such a shape.
+// Few output columns (a router's logits): one warp per ROW, 16 columns at a time in registers; lanes stride over k, fp32
+// multiply-add, the lanes' partial sums added in a fixed tree.  The row is read once per 16 columns and W stays in L1 / L2 —
+// the tile kernel above would leave all but a handful of SMs idle on such a shape.
 template <typename AT, typename WT, typename CT>
 __global__ void __launch_bounds__(256) linear_dot_kernel(LinArgs p) {
-  const int64_t o = blockIdx.x * (int64_t) 8 + threadIdx.x / 32;
-  if (o >= (int64_t) p.M * p.N) return;
-  const int m = (int) (o / p.N), n = (int) (o % p.N), lane = threadIdx.x % 32;
+  const int m = blockIdx.x * 8 + threadIdx.x / 32, lane = threadIdx.x % 32;
+  if (m >= p.M) return;
   const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) m * p.lda;
-  const WT* W = reinterpret_cast<const WT*>(p.w) + (int64_t) n * p.K;
-  float acc = 0.f;
-  for (int k = lane; k < p.K; k += 32) acc = fmaf(to_f<AT>(A[k]), to_f<WT>(W[k]), acc);
-  acc = warp_sum(acc);
-  if (lane == 0) {
-    if (p.bias) acc += to_f<WT>(reinterpret_cast<const WT*>(p.bias)[n]);
-    reinterpret_cast<CT*>(p.c)[(int64_t) m * p.ldc + n] = from_f<CT>(apply_act(acc, p.act));
+  const WT* W = reinterpret_cast<const WT*>(p.w);
+  for (int n0 = 0; n0 < p.N; n0 += 16) {
+    float acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+    for (int k = lane; k < p.K; k += 32) {
+      const float av = to_f<AT>(A[k]);
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (n0 + j < p.N) acc[j] = fmaf(av, to_f<WT>(W[(int64_t) (n0 + j) * p.K + k]), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float v = warp_sum(acc[j]);
+      if (lane == 0 && n0 + j < p.N) {
+        float r = v;
+        if (p.bias) r += to_f<WT>(reinterpret_cast<const WT*>(p.bias)[n0 + j]);
+        reinterpret_cast<CT*>(p.c)[(int64_t) m * p.ldc + n0 + j] = from_f<CT>(apply_act(r, p.act));
+      }
+    }
   }
 }
 
 template <typename AT, typename WT>
 int launch_dot(const LinArgs& p, int c_dtype, cudaStream_t s) {
-  const unsigned grid = (unsigned) (((int64_t) p.M * p.N + 7) / 8);
+  const unsigned grid = (unsigned) ((p.M + 7) / 8);
   if (c_dtype == TB_DT_F32) linear_dot_kernel<AT, WT, float><<<grid, 256, 0, s>>>(p);
   else linear_dot_kernel<AT, WT, __nv_bfloat16><<<grid, 256, 0, s>>>(p);
   return 0;

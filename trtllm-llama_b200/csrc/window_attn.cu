@@ -40,7 +40,7 @@ __device__ __forceinline__ float ld_w(const void* p, int dtype, int64_t i) {
                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
 }
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 
 struct QkvArgs {
   const float* proj; int64_t ldp;            // [rows, >= C] : q (H dim) | k (G dim) | v (G vdim)
@@ -249,7 +249,9 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
   const int e = blockIdx.y, g = blockIdx.z;
   const int per = a.H / a.G, len = m.seq_len[e], past = m.seq_past[e], row0 = m.seq_start[e];
   const int split = m.nsplit > 1 ? blockIdx.x % m.nsplit : 0, nsplit = m.nsplit > 1 ? m.nsplit : 1;
-  const int r0 = (blockIdx.x / nsplit) * kMmaRows;      // first (token, head) row of this CTA
+  // row blocks are dealt from the END of the portion: the blocks at its start see the fewest keys, so the cheap CTAs
+  // fill the last, partial wave of the grid instead of the expensive ones
+  const int r0 = ((int) (gridDim.x / nsplit) - 1 - (int) (blockIdx.x / nsplit)) * kMmaRows;   // first (token, head) row of this CTA
   if (r0 >= len * per) return;
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gq = lane / 4, tq = lane % 4;
   const int t_first = r0 / per;
