@@ -124,42 +124,73 @@ __global__ void __launch_bounds__(256) linear_fma_kernel(LinArgs p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Few output columns (a router's logits): one warp per ROW, 16 columns at a time in registers; lanes stride over k, fp32
-// multiply-add, the lanes' partial sums added in a fixed tree.  The row is read once per 16 columns and W stays in L1 / L2 —
-// the tile kernel above would leave all but a handful of SMs idle on such a shape.
+// Few output columns (a router's logits): one CTA per ROW, 16 columns at a time in registers; the 256 threads stride over
+// k in fp32 multiply-adds, then the partial sums are added in a fixed tree (lanes, then the eight warps in order).  The row is
+// read once per 16 columns and W stays in L1 / L2 — the tile kernel above would leave all but a handful of SMs idle here.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+
 template <typename AT, typename WT, typename CT>
-__global__ void __launch_bounds__(256) linear_dot_kernel(LinArgs p) {
-  const int m = blockIdx.x * 8 + threadIdx.x / 32, lane = threadIdx.x % 32;
-  if (m >= p.M) return;
+__global__ void __launch_bounds__(256) linear_dot_kernel(LinArgs p, int vec) {
+  __shared__ float part[8][16];
+  const int m = blockIdx.x, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const AT* A = reinterpret_cast<const AT*>(p.a) + (int64_t) m * p.lda;
   const WT* W = reinterpret_cast<const WT*>(p.w);
   for (int n0 = 0; n0 < p.N; n0 += 16) {
     float acc[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-    for (int k = lane; k < p.K; k += 32) {
-      const float av = to_f<AT>(A[k]);
+    if (vec) {               // 8 | K, 16-byte aligned rows: a thread takes 8 consecutive k per trip
+      for (int k = threadIdx.x * 8; k < p.K; k += 256 * 8) {
+        float av[8];
+        load8(A + k, av);
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        if (n0 + j < p.N) acc[j] = fmaf(av, to_f<WT>(W[(int64_t) (n0 + j) * p.K + k]), acc[j]);
+        for (int j = 0; j < 16; ++j) {
+          if (n0 + j >= p.N) break;
+          float wv[8];
+          load8(W + (int64_t) (n0 + j) * p.K + k, wv);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[j] = fmaf(av[i], wv[i], acc[j]);
+        }
+      }
+    } else {
+      for (int k = threadIdx.x; k < p.K; k += 256) {
+        const float av = to_f<AT>(A[k]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (n0 + j < p.N) acc[j] = fmaf(av, to_f<WT>(W[(int64_t) (n0 + j) * p.K + k]), acc[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float v = warp_sum(acc[j]);
-      if (lane == 0 && n0 + j < p.N) {
-        float r = v;
-        if (p.bias) r += to_f<WT>(reinterpret_cast<const WT*>(p.bias)[n0 + j]);
-        reinterpret_cast<CT*>(p.c)[(int64_t) m * p.ldc + n0 + j] = from_f<CT>(apply_act(r, p.act));
-      }
+      if (lane == 0) part[warp][j] = v;
     }
+    __syncthreads();
+    if (threadIdx.x < 16 && n0 + threadIdx.x < p.N) {
+      float r = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) r += part[w][threadIdx.x];
+      if (p.bias) r += to_f<WT>(reinterpret_cast<const WT*>(p.bias)[n0 + threadIdx.x]);
+      reinterpret_cast<CT*>(p.c)[(int64_t) m * p.ldc + n0 + threadIdx.x] = from_f<CT>(apply_act(r, p.act));
+    }
+    __syncthreads();
   }
 }
 
 template <typename AT, typename WT>
 int launch_dot(const LinArgs& p, int c_dtype, cudaStream_t s) {
-  const unsigned grid = (unsigned) ((p.M + 7) / 8);
-  if (c_dtype == TB_DT_F32) linear_dot_kernel<AT, WT, float><<<grid, 256, 0, s>>>(p);
-  else linear_dot_kernel<AT, WT, __nv_bfloat16><<<grid, 256, 0, s>>>(p);
+  const int vec = p.K % 8 == 0 && (uintptr_t) p.a % 16 == 0 && (uintptr_t) p.w % 16 == 0 && (p.lda * sizeof(AT)) % 16 == 0;
+  if (c_dtype == TB_DT_F32) linear_dot_kernel<AT, WT, float><<<p.M, 256, 0, s>>>(p, vec);
+  else linear_dot_kernel<AT, WT, __nv_bfloat16><<<p.M, 256, 0, s>>>(p, vec);
   return 0;
 }
 

@@ -5,7 +5,7 @@
 // Pool entry of one position: [G][dim] rotated keys, then [G][vdim] values (G key/value heads).  Query head h reads
 // key/value head h / (H / G).
 //
-//   qkv_conv_rope_append_kernel   one thread per (row, channel; rows along grid x) of the concatenated q | k | v projection: the causal
+//   qkv_conv_rope_append_kernel   one CTA per row, threads walk pairs of channels of the concatenated q | k | v projection: the causal
 //                                 convolution over the row's own portion and the sequence's carried inputs, the
 //                                 rotation of the head's leading `dims` elements (interleaved pairs; the partner's
 //                                 convolution is recomputed), and the store: queries to their buffer, keys and values
@@ -20,6 +20,7 @@
 // unscaled, whatever the number of key blocks.  Keys are visited in an order fixed by the row's position alone.
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -64,36 +65,35 @@ __device__ __forceinline__ float conv_at(const QkvArgs& a, const float* st, int 
   return acc;
 }
 
-// one thread per (row, pair of neighbouring channels): both convolutions once, the rotation, one 2-element store
+// one CTA (or a few, for steps of few rows) per row; a thread walks pairs of neighbouring channels (both convolutions once, the rotation, the two stores),
+// the row's place in its sequence and its page looked up once per thread
 template <typename T>
-__global__ void qkv_conv_rope_append_kernel(T* q_out, T* pool, QkvArgs a) {
+__global__ void __launch_bounds__(256) qkv_conv_rope_append_kernel(T* q_out, T* pool, QkvArgs a) {
   const int Cq = a.H * a.dim, Ck = a.G * a.dim, Cv = a.G * a.vdim, C = Cq + Ck + Cv;
-  const int row = blockIdx.x, ch = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
-  if (ch >= C) return;
+  const int row = blockIdx.x;
   const int e = a.tok_seq[row], pos = a.tok_pos[row], past = a.seq_past[e], start = a.seq_start[e];
   const float* st = a.state + (int64_t) a.seq_slot[e] * (a.taps - 1) * C;
-  const bool two = ch + 1 < C;
-  float y0 = conv_at(a, st, C, ch, pos, past, start), y1 = two ? conv_at(a, st, C, ch + 1, pos, past, start) : 0.f;
-  if (ch < Cq + Ck) {
-    const int d = (ch < Cq ? ch : ch - Cq) % a.dim;      // even: a.dim is even whenever anything is rotated
-    if (d < a.dims) {
-      const float* cs = a.table + ((int64_t) row * (a.dims / 2) + d / 2) * 2;
-      const float u = y0, v = y1;
-      y0 = fmaf(u, cs[0], -v * cs[1]);
-      y1 = fmaf(v, cs[0], u * cs[1]);
+  const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
+  T* q_row = q_out + (int64_t) row * Cq;
+  T* kv_row = pool + slot * (Ck + Cv);
+  const float* cs_row = a.dims > 0 ? a.table + (int64_t) row * a.dims : nullptr;      // [dims / 2][cos, sin]
+#pragma unroll 2
+  for (int ch = 2 * (blockIdx.y * 256 + threadIdx.x); ch < C; ch += 2 * 256 * gridDim.y) {
+    const bool two = ch + 1 < C;
+    float y0 = conv_at(a, st, C, ch, pos, past, start), y1 = two ? conv_at(a, st, C, ch + 1, pos, past, start) : 0.f;
+    if (ch < Cq + Ck) {
+      const int d = (ch < Cq ? ch : ch - Cq) % a.dim;    // even: a.dim is even whenever anything is rotated
+      if (d < a.dims) {
+        const float c = cs_row[d], sn = cs_row[d + 1];
+        const float u = y0, v = y1;
+        y0 = fmaf(u, c, -v * sn);
+        y1 = fmaf(v, c, u * sn);
+      }
     }
-  }
-  // q | k | v boundaries may be odd only when nothing is rotated: store the two elements one by one
-  #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int c = ch + i;
-    if (c >= C) break;
-    const float y = i ? y1 : y0;
-    if (c < Cq) {
-      q_out[(int64_t) row * Cq + c] = from_f<T>(y);
-    } else {
-      const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
-      pool[slot * (Ck + Cv) + (c - Cq)] = from_f<T>(y);
+    // the q | k | v boundaries can be odd only when nothing is rotated: the two elements are stored one by one
+    if (ch < Cq) q_row[ch] = from_f<T>(y0); else kv_row[ch - Cq] = from_f<T>(y0);
+    if (two) {
+      if (ch + 1 < Cq) q_row[ch + 1] = from_f<T>(y1); else kv_row[ch + 1 - Cq] = from_f<T>(y1);
     }
   }
 }
@@ -446,25 +446,31 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
 
 // one CTA per (row, head): splits merged in index order, the sink added once, gate applied
 __global__ void window_attention_merge_kernel(__nv_bfloat16* out, const float* partial, AttnArgs a, int nsplit, int vdim) {
+  __shared__ float w_s[32];                    // weight of every split: 2^(m_s - M), 0 for a split that saw nothing
+  __shared__ float f_s;
   const int row = blockIdx.x, head = blockIdx.y;
   const float* src = partial + ((int64_t) row * a.H + head) * nsplit * (vdim + 2);
-  const float sink2 = a.sink ? ld_w(a.sink, a.sink_dtype, head) * 1.4426950408889634f : -INFINITY;
-  float M = sink2;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, src[s * (vdim + 2)]);
-  float l = a.sink ? exp2f(sink2 - M) : 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float ms = src[s * (vdim + 2)];
-    if (ms != -INFINITY) l += src[s * (vdim + 2) + 1] * exp2f(ms - M);
+  if (threadIdx.x < 32) {
+    const int s = threadIdx.x;
+    const float ms = s < nsplit ? src[s * (vdim + 2)] : -INFINITY, ls = s < nsplit ? src[s * (vdim + 2) + 1] : 0.f;
+    const float sink2 = a.sink ? ld_w(a.sink, a.sink_dtype, head) * 1.4426950408889634f : -INFINITY;
+    const float M = fmaxf(warp_max(ms), sink2);                  // finite: the row sees at least itself
+    const float w = ms == -INFINITY ? 0.f : exp2f(ms - M);
+    w_s[s] = w;
+    float l = ls * w;
+    // fixed order: lanes are added in a tree whose shape does not depend on the data
+    l = warp_sum(l) + (a.sink ? exp2f(sink2 - M) : 0.f);
+    if (s == 0) {
+      float f = 1.f / l;
+      if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) row * a.ldg + head]));
+      f_s = f;
+    }
   }
-  float f = 1.f / l;
-  if (a.gate) f *= 1.f / (1.f + expf(-a.gate[(int64_t) row * a.ldg + head]));
+  __syncthreads();
   for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const float ms = src[s * (vdim + 2)];
-      if (ms != -INFINITY) acc = fmaf(src[s * (vdim + 2) + 2 + c], exp2f(ms - M), acc);
-    }
-    out[((int64_t) row * a.H + head) * vdim + c] = __float2bfloat16_rn(acc * f);
+    for (int s = 0; s < nsplit; ++s) acc = fmaf(src[s * (vdim + 2) + 2 + c], w_s[s], acc);
+    out[((int64_t) row * a.H + head) * vdim + c] = __float2bfloat16_rn(acc * f_s);
   }
 }
 
@@ -506,9 +512,10 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
   if (rows == 0) return 0;
   QkvArgs a{proj, ldp, conv_w, w_dtype, state, table, tok_seq, tok_pos, seq_start, seq_past, seq_slot, block_table,
             max_blocks, page, rows, heads, kv_heads, dim, vdim, dims, taps};
+  // one CTA per row when the rows alone fill the chip; a step of few rows also spreads a row's channels over CTAs
   const int C = heads * dim + kv_heads * (dim + vdim);
-  if ((C + 511) / 512 > 65535) return -2;
-  const dim3 grid(rows, (C + 511) / 512);
+  const int ysplit = rows >= 296 ? 1 : std::min((C + 511) / 512, (296 + rows - 1) / rows);
+  const dim3 grid(rows, ysplit);
   if (dtype == TB_DT_F32) qkv_conv_rope_append_kernel<float><<<grid, 256, 0, (cudaStream_t) stream>>>((float*) q_out, (float*) pool, a);
   else qkv_conv_rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t) stream>>>((__nv_bfloat16*) q_out, (__nv_bfloat16*) pool, a);
   TB_CHECK_CUDA(cudaGetLastError());
