@@ -392,3 +392,35 @@ def test_registry_and_trace_tool_end_to_end(tmp_path):
     _close(got0, want["a"][[0, 29]], torch.float32, "trace step 0", scale=2.0)
     _close(got1, torch.stack([want["a"][30], want["b"][8]]), torch.float32, "trace step 1", scale=2.0)
     assert not os.path.exists(tmp_path / "o" / "2.f32")
+
+
+def test_generation_example_from_the_command_line(tmp_path):
+    """examples/inflight/run.py on a Nililix folder: the registry picks the class, the scheduler runs the prompts, and the
+    ids are the oracle's greedy continuation."""
+    import csv
+    import subprocess
+    import sys
+    from trtllm_llama_b200.checkpoint import write_safetensors
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, t = O.random_nililix(**STACKS["tc-dense"])
+    os.makedirs(tmp_path / "m")
+    with open(tmp_path / "m" / "config.json", "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(str(tmp_path / "m" / "model.safetensors"), t)
+    prompts = [_tokens(n, cfg["vocab"], 70 + n) for n in (5, 31)]
+    with open(tmp_path / "in.csv", "w") as f:
+        csv.writer(f).writerows(prompts)
+    r = subprocess.run([sys.executable, os.path.join(root, "examples", "inflight", "run.py"), "--model_dir", str(tmp_path / "m"),
+                        "--input_tokens", str(tmp_path / "in.csv"), "--max_output_len", "6", "--dtype", "float32",
+                        "--output_csv", str(tmp_path / "out.csv"), "--max_step_tokens", "16"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    with open(tmp_path / "out.csv") as f:
+        outs = [[int(x) for x in row] for row in csv.reader(f) if row]
+    assert len(outs) == 2
+    for p, o in zip(prompts, outs):
+        o = o[-6:]
+        lg = O.nililix_forward(cfg, t, p + o[:-1])[len(p) - 1:]
+        for i, tok in enumerate(o):
+            best = lg[i].topk(2)
+            if int(best.indices[0]) != tok:
+                assert float(best.values[0] - lg[i][tok]) <= 2 * TOL[torch.float32] * float(lg.abs().max()), f"step {i}: id {tok}"
