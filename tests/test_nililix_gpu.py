@@ -258,6 +258,43 @@ def test_one_key_stands_out(dtype, where, window, dist):
     _close(torch.cat(outs), want, dtype, f"window {window}, key {dist} back ({where})")
 
 
+@pytest.mark.parametrize("window", [0, 200, 64])
+@pytest.mark.parametrize("d,dv,H,G", [(32, 16, 4, 2), (32, 32, 3, 3), (64, 32, 6, 1), (64, 64, 8, 2), (96, 96, 2, 1), (128, 64, 10, 2),
+                                      (128, 128, 8, 2), (48, 24, 4, 2)])
+def test_attention_operator_head_sizes(d, dv, H, G, window):
+    """Every head size the tensor-core kernel is built for (and one it is not): a prompt of 300 positions over shuffled
+    pages, then three tokens decoded one by one — few rows over a long context, so their key tiles are dealt to several
+    CTAs and merged — against the plain formula and against the SIMT kernel."""
+    from trtllm_llama_b200 import ops
+    from trtllm_llama_b200.inflight import RaggedBatch
+    page, P, dt = 16, 303, torch.bfloat16
+    g = torch.Generator().manual_seed(d * 7 + dv + window)
+    q, k, v = torch.randn(P, H, d, generator=g).to(dt), torch.randn(P, G, d, generator=g).to(dt), torch.randn(P, G, dv, generator=g).to(dt)
+    sink, gate = torch.randn(H, generator=g).to(dt), torch.randn(P, H, generator=g)
+    want = O.windowed_sink_attention(q.double(), k.double(), v.double(), d ** -0.5, window, sink.double()) * torch.sigmoid(gate.double())[:, :, None]
+    proj = torch.cat([q.reshape(P, -1), k.reshape(P, -1), v.reshape(P, -1)], dim=1).float().cuda()
+    conv_w = torch.ones(proj.shape[1], 1, dtype=dt, device="cuda")
+    nblk = -(-P // page)
+    blocks = torch.randperm(nblk, generator=g).tolist()
+    outs = {}
+    for simt in (False, True):
+        ops.FORCE_SIMT_ATTENTION = simt
+        try:
+            pool = torch.full((nblk * page, G * (d + dv)), float("nan"), dtype=dt, device="cuda")
+            at, rows = 0, []
+            for n in [P - 3, 1, 1, 1]:
+                b = RaggedBatch([([0] * n, at, 0, blocks)], [], "cuda")
+                qq = ops.qkv_conv_rope_append(proj[at:at + n], conv_w, None, None, 0, pool, b, page, H, G, d, dv)
+                rows.append(ops.window_attention(qq, pool, b, page, G, dv, d ** -0.5, window, sink=sink.cuda(), gate=gate[at:at + n].cuda()))
+                at += n
+            outs[simt] = torch.cat(rows)
+        finally:
+            ops.FORCE_SIMT_ATTENTION = False
+    _close(outs[True], want, dt, f"SIMT attention {d}/{dv}", scale=0.5)
+    _close(outs[False], want, dt, f"attention {d}/{dv}, window {window}", scale=0.5)
+    assert bool(ops._rl.tb_window_attention_tensor_cores(ops.DT_BF16, H, G, d, dv)) == ((d, dv) != (48, 24))
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------------------------
