@@ -87,9 +87,9 @@ int tb_gated_act(void* out, int out_dtype, const float* gu, int rows, int ff, fl
 
 /* cos / sin of pos * base^(-2 i / dims), i < dims / 2, for every row: table fp32 [N, dims / 2, 2] (angles in fp64). */
 int tb_rope_table(float* table, const int* tok_pos, int rows, int dims, double base, tb_stream_t stream);
-/* The same with scaled frequencies (factor > 0): a frequency whose wavelength l = 2 pi / f exceeds original / low becomes
- * f / factor, one with l < original / high stays, and between the two f' = (1 - s) f / factor + s f with
- * s = (original / l - low) / (high - low). */
+/* The same with scaled frequencies (factor > 0): with wavelength lambda = 2 pi / f, frequencies with lambda above
+ * original / low are divided by factor, those with lambda below original / high are kept, and in the band between a share
+ * keep = (original / lambda - low) / (high - low) of the frequency is kept: f' = f * (keep + (1 - keep) / factor). */
 int tb_rope_table_scaled(float* table, const int* tok_pos, int rows, int dims, double base, double factor, double low,
                          double high, double original, tb_stream_t stream);
 
@@ -148,7 +148,7 @@ int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, cons
  *
  * tb_qkv_conv_rope_append: proj fp32 [N, ldp] holds per row q (heads * dim) | k (kv_heads * dim) | v (kv_heads * vdim)
  * = C channels (further columns are ignored).  Each channel runs a causal convolution of `taps` taps (conv_w [C, taps],
- * no bias; y_t = sum_j w[:, j] u_(t - taps + 1 + j)) over the row's portion and the carried inputs state[slot] (fp32
+ * no bias; tap j weighs the input taps - 1 - j positions back) over the row's portion and the carried inputs state[slot] (fp32
  * [slots, taps - 1, C], oldest first; zeros before the sequence's start); then the first `dims` elements of every query
  * and key head are rotated as interleaved pairs (2i, 2i + 1) by the row's table entry.  Queries go to q_out T [N, heads,
  * dim]; keys and values to the row's position in its sequence's pages.  Carry the state on with

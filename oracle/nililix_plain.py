@@ -20,14 +20,15 @@ def rms_norm(x, w, eps):
 
 
 def short_conv(u, w):
-    """u [T, C], w [C, taps]: y_t = sum_j w[:, j] * u_(t - taps + 1 + j), zeros before position 0."""
+    """u [T, C], w [C, taps]: tap j weighs the input ``taps - 1 - j`` positions back (the last tap the current one); inputs
+    before position 0 are zero."""
     T, taps = u.shape[0], w.shape[1]
     y = torch.zeros_like(u)
     for t in range(T):
         for j in range(taps):
-            src = t - taps + 1 + j
-            if src >= 0:
-                y[t] += w[:, j] * u[src]
+            back = taps - 1 - j
+            if t - back >= 0:
+                y[t] += w[:, j] * u[t - back]
     return y
 
 
@@ -45,8 +46,8 @@ def rotary_frequencies(dims, base, scaling=None):
             elif wavelength > orig / low:
                 f = f / factor
             else:
-                s = (orig / wavelength - low) / (high - low)
-                f = (1.0 - s) * f / factor + s * f
+                keep = (orig / wavelength - low) / (high - low)       # 0 at the slow end of the band, 1 at the fast end
+                f = f * (keep + (1.0 - keep) / factor)
         out.append(f)
     return out
 

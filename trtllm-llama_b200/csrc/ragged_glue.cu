@@ -128,8 +128,8 @@ __global__ void rope_table_kernel(float* table, const int* tok_pos, int rows, in
     if (wavelength > original / low) {
       freq /= factor;
     } else if (!(wavelength < original / high)) {
-      const double s = (original / wavelength - low) / (high - low);
-      freq = (1.0 - s) * freq / factor + s * freq;
+      const double keep = (original / wavelength - low) / (high - low);     // 0 at the slow end of the band, 1 at the fast end
+      freq *= keep + (1.0 - keep) / factor;
     }
   }
   double s, c;

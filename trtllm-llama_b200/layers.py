@@ -119,7 +119,8 @@ class WindowedAttention:
 
     q = W_q h, k = W_k h, v = W_v h (``heads`` query heads and ``kv_heads`` key/value heads of size ``dim``; values of
     size ``vdim``; query head i reads key/value head i // (heads / kv_heads)).  Every channel of q, k and v then runs a
-    causal convolution over time with ``taps`` taps (y_t = sum_j c[:, j] u_(t - taps + 1 + j)), and the first
+    causal convolution over time with ``taps`` taps (tap j weighs the input taps - 1 - j positions back; tap taps - 1 the
+    current one), and the first
     ``rot_dims`` elements of each query and key head are rotated as interleaved pairs (2i, 2i + 1) by position times
     base^(-2i / rot_dims), optionally with the long wavelengths slowed (``rot_scaling`` = (factor, low, high, original)).
     score(i, j) = scale * q_i . k_j for 0 <= i - j < window (window 0: all j <= i); the softmax denominator holds one
