@@ -128,9 +128,10 @@ int tb_causal_conv1d(float* out, const float* x, const void* w, const void* bias
                      const int* tok_seq, const int* tok_pos, const int* seq_start, const int* seq_past,
                      const int* seq_slot, int rows, int channels, int taps, tb_stream_t stream);
 /* state[slot] <- the last taps - 1 inputs of (what it held ++ this step's rows); run after the convolution.  x has row
- * stride ldx (its first `channels` columns are the convolution's inputs). */
+ * stride ldx (its first `channels` columns are the convolution's inputs).  skip_single != 0: sequences that bring one row
+ * are left alone (tb_qkv_conv_rope_append has moved them on). */
 int tb_causal_conv1d_update(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len, const int* seq_past,
-                            const int* seq_slot, int seqs, int channels, int taps, tb_stream_t stream);
+                            const int* seq_slot, int seqs, int channels, int taps, int skip_single, tb_stream_t stream);
 
 /* Real-gated linear recurrent unit over a ragged batch.  gates fp32 [N, blocks, 2, C / blocks]: per block the
  * recurrence-gate logits, then the input-gate logits (biases already added).  Per channel, in sequence order:
@@ -152,12 +153,14 @@ int tb_rglru_scan(void* out, int dtype, const float* u, const float* gates, cons
  * [slots, taps - 1, C], oldest first; zeros before the sequence's start); then the first `dims` elements of every query
  * and key head are rotated as interleaved pairs (2i, 2i + 1) by the row's table entry.  Queries go to q_out T [N, heads,
  * dim]; keys and values to the row's position in its sequence's pages.  Carry the state on with
- * tb_causal_conv1d_update(state, proj, ldp, ..., C, taps) afterwards. */
+ * tb_causal_conv1d_update(state, proj, ldp, ..., C, taps, skip_single) afterwards.  state_rw == state with seq_len given: a
+ * sequence that brings ONE row has its carried inputs moved on by this kernel (the thread that read a channel's inputs
+ * rewrites them), the update is then called with skip_single = 1 — or not at all when every sequence brings one row. */
 int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* proj, int64_t ldp, const void* conv_w,
                             int w_dtype, const float* state, const float* table, int dims, const int* tok_seq,
                             const int* tok_pos, const int* seq_start, const int* seq_past, const int* seq_slot,
                             const int* block_table, int max_blocks, int page, int rows, int heads, int kv_heads, int dim,
-                            int vdim, int taps, tb_stream_t stream);
+                            int vdim, int taps, float* state_rw, const int* seq_len, tb_stream_t stream);
 
 /* Attention of every row over the cached positions j of its sequence with 0 <= pos - j < window (window 0: all of
  * 0..pos).  Query head h uses key/value head h / (heads / kv_heads).  score = scale * <q, k>; the softmax denominator

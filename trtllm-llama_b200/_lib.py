@@ -198,10 +198,10 @@ RAGGED_SIGNATURES = {
     "tb_latent_attention": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, i32, vp, vp]),
     "tb_latent_attention_tensor_cores": (i32, [i32, i32, i32]),
     "tb_causal_conv1d": (i32, [vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]),
-    "tb_causal_conv1d_update": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, vp]),
+    "tb_causal_conv1d_update": (i32, [vp, vp, i64, vp, vp, vp, vp, i32, i32, i32, i32, vp]),
     "tb_rglru_scan": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, f32, i32, vp, vp]),
     "tb_qkv_conv_rope_append": (i32, [vp, vp, i32, vp, i64, vp, i32, vp, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
-                                      i32, i32, i32, i32, vp]),
+                                      i32, i32, i32, i32, vp, vp, vp]),
     "tb_window_attention_tensor_cores": (i32, [i32, i32, i32, i32, i32]),
     "tb_window_attention": (i32, [vp, vp, vp, i32, vp, i64, vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32,
                                   i32, i32, f32, i32, i32, i32, vp, vp]),

@@ -42,11 +42,13 @@ __global__ void causal_conv1d_kernel(float* out, const float* x, const void* w, 
 
 // one thread per (sequence, channel): reads every old value it needs before it writes
 __global__ void causal_conv1d_update_kernel(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len,
-                                            const int* seq_past, const int* seq_slot, int seqs, int channels, int taps) {
+                                            const int* seq_past, const int* seq_slot, int seqs, int channels, int taps,
+                                            int skip_single) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= seqs * channels) return;
   const int e = i / channels, ch = i % channels;
   const int len = seq_len[e], past = seq_past[e], start = seq_start[e];
+  if (skip_single && len == 1) return;               // the convolution kernel moved this sequence's inputs on itself
   float* st = state + (int64_t) seq_slot[e] * (taps - 1) * channels;
   float keep[kMaxTaps];
   const int n = taps - 1;
@@ -179,14 +181,14 @@ extern "C" int tb_causal_conv1d(float* out, const float* x, const void* w, const
 
 extern "C" int tb_causal_conv1d_update(float* state, const float* x, int64_t ldx, const int* seq_start, const int* seq_len,
                                        const int* seq_past, const int* seq_slot, int seqs, int channels, int taps,
-                                       tb_stream_t stream) {
+                                       int skip_single, tb_stream_t stream) {
   if (!state || !x || !seq_start || !seq_len || !seq_past || !seq_slot || channels <= 0 || taps < 1 || taps > kMaxTaps ||
       seqs < 0)
     return -1;
   if (seqs == 0 || taps == 1) return 0;
   const int n = seqs * channels;
   causal_conv1d_update_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t) stream>>>(state, x, ldx, seq_start, seq_len, seq_past,
-                                                                                   seq_slot, seqs, channels, taps);
+                                                                                   seq_slot, seqs, channels, taps, skip_single);
   TB_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

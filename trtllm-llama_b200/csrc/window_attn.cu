@@ -50,6 +50,8 @@ struct QkvArgs {
   const float* table;                        // [rows, dims / 2, 2] cos, sin
   const int *tok_seq, *tok_pos, *seq_start, *seq_past, *seq_slot, *block_table;
   int max_blocks, page, rows, H, G, dim, vdim, dims, taps;
+  float* state_rw;                           // == state when a sequence that brings ONE row moves its carried inputs on here
+  const int* seq_len;                        // (then tb_causal_conv1d_update skips such sequences)
 };
 
 // convolution output of channel ch at the row's position
@@ -76,6 +78,10 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_append_kernel(T* q_out, T* 
   const int64_t slot = (int64_t) a.block_table[(int64_t) e * a.max_blocks + pos / a.page] * a.page + pos % a.page;
   T* q_row = q_out + (int64_t) row * Cq;
   T* kv_row = pool + slot * (Ck + Cv);
+  // a sequence that brings one row: nobody else reads its carried inputs in this step, and this thread is the only one that
+  // touches its channels — it moves them on itself, after it has read them
+  const bool carry = a.state_rw && a.taps > 1 && a.seq_len[e] == 1;
+  float* st_rw = carry ? a.state_rw + (int64_t) a.seq_slot[e] * (a.taps - 1) * C : nullptr;
   const float* cs_row = a.dims > 0 ? a.table + (int64_t) row * a.dims : nullptr;      // [dims / 2][cos, sin]
 #pragma unroll 2
   for (int ch = 2 * (blockIdx.y * 256 + threadIdx.x); ch < C; ch += 2 * 256 * gridDim.y) {
@@ -94,6 +100,15 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_append_kernel(T* q_out, T* 
     if (ch < Cq) q_row[ch] = from_f<T>(y0); else kv_row[ch - Cq] = from_f<T>(y0);
     if (two) {
       if (ch + 1 < Cq) q_row[ch + 1] = from_f<T>(y1); else kv_row[ch + 1 - Cq] = from_f<T>(y1);
+    }
+    if (carry) {
+      const int n = a.taps - 1;
+      for (int i = 0; i < (two ? 2 : 1); ++i) {
+        const int c = ch + i;
+        // row j of the new state holds position pos - n + 1 + j: the old row j + 1 (zero before the sequence's start), then this row's input
+        for (int j = 0; j + 1 < n; ++j) st_rw[(int64_t) j * C + c] = pos - n + 1 + j >= 0 ? st_rw[(int64_t) (j + 1) * C + c] : 0.f;
+        st_rw[(int64_t) (n - 1) * C + c] = a.proj[(int64_t) row * a.ldp + c];
+      }
     }
   }
 }
@@ -502,7 +517,7 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
                                        int w_dtype, const float* state, const float* table, int dims, const int* tok_seq,
                                        const int* tok_pos, const int* seq_start, const int* seq_past, const int* seq_slot,
                                        const int* block_table, int max_blocks, int page, int rows, int heads, int kv_heads,
-                                       int dim, int vdim, int taps, tb_stream_t stream) {
+                                       int dim, int vdim, int taps, float* state_rw, const int* seq_len, tb_stream_t stream) {
   if (!q_out || !pool || !proj || !conv_w || !tok_seq || !tok_pos || !seq_start || !seq_past || !seq_slot || !block_table)
     return -1;
   if ((dtype != TB_DT_F32 && dtype != TB_DT_BF16) || (w_dtype != TB_DT_F32 && w_dtype != TB_DT_BF16)) return -1;
@@ -510,8 +525,9 @@ extern "C" int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const
       rows < 0 || dims < 0 || dims % 2 || dims > dim || (dims > 0 && (dim % 2 || !table)) || (taps > 1 && !state))
     return -1;
   if (rows == 0) return 0;
+  if (state_rw && (state_rw != state || !seq_len)) return -1;
   QkvArgs a{proj, ldp, conv_w, w_dtype, state, table, tok_seq, tok_pos, seq_start, seq_past, seq_slot, block_table,
-            max_blocks, page, rows, heads, kv_heads, dim, vdim, dims, taps};
+            max_blocks, page, rows, heads, kv_heads, dim, vdim, dims, taps, state_rw, seq_len};
   // one CTA per row when the rows alone fill the chip; a step of few rows also spreads a row's channels over CTAs
   const int C = heads * dim + kv_heads * (dim + vdim);
   const int ysplit = rows >= 296 ? 1 : std::min((C + 511) / 512, (296 + rows - 1) / rows);

@@ -525,7 +525,7 @@ def causal_conv1d(x, w, bias, state, batch):
                                _p(batch.seq_start), _p(batch.seq_past), _p(batch.seq_slot), rows, ch, taps, _stream()),
           "tb_causal_conv1d")
     check(_rl.tb_causal_conv1d_update(_p(state), _p(x), x.stride(0), _p(batch.seq_start), _p(batch.seq_len), _p(batch.seq_past),
-                                      _p(batch.seq_slot), batch.num_seqs, ch, taps, _stream()), "tb_causal_conv1d_update")
+                                      _p(batch.seq_slot), batch.num_seqs, ch, taps, 0, _stream()), "tb_causal_conv1d_update")
     return out
 
 
@@ -582,10 +582,12 @@ def qkv_conv_rope_append(proj, conv_w, state, table, dims, pool, batch, page, he
     check(_rl.tb_qkv_conv_rope_append(_p(q), _p(pool), _dt(pool), _p(proj), proj.stride(0), _p(conv_w), _dt(conv_w),
                                       _p(state), _p(table), dims, _p(batch.tok_seq), _p(batch.tok_pos), _p(batch.seq_start),
                                       _p(batch.seq_past), _p(batch.seq_slot), _p(batch.block_table), batch.max_blocks, page,
-                                      rows, heads, kv_heads, dim, vdim, taps, _stream()), "tb_qkv_conv_rope_append")
-    if taps > 1:
+                                      rows, heads, kv_heads, dim, vdim, taps, _p(state) if taps > 1 else None,
+                                      _p(batch.seq_len) if taps > 1 else None, _stream()), "tb_qkv_conv_rope_append")
+    # sequences that bring one row were moved on by the kernel above; a generation step needs nothing more
+    if taps > 1 and batch.max_len > 1:
         check(_rl.tb_causal_conv1d_update(_p(state), _p(proj), proj.stride(0), _p(batch.seq_start), _p(batch.seq_len),
-                                          _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, C, taps, _stream()),
+                                          _p(batch.seq_past), _p(batch.seq_slot), batch.num_seqs, C, taps, 1, _stream()),
               "tb_causal_conv1d_update")
     return q
 
