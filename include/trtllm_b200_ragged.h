@@ -167,7 +167,7 @@ int tb_qkv_conv_rope_append(void* q_out, void* pool, int dtype, const float* pro
  * also holds exp(sink[h]) (sink fp32 or bf16 [heads], or NULL for none): a term without key or value, not scaled.
  * out T [N, heads, vdim] = softmax-weighted values, times sigmoid(gate[n, h]) when gate (fp32 logits, row stride ldg) is
  * given.  Softmax in fp32; keys are visited in blocks of 32 absolute positions from the window's first block, so a row's
- * result does not depend on how its prompt was cut or on the batch around it.  vdim <= 256.
+ * result does not depend on how its prompt was cut or on the batch around it.  vdim <= 512.
  * bf16 with a (dim, vdim) pair the tensor-core kernel is built for (tb_window_attention_tensor_cores tells) runs on
  * tensor cores when the per-sequence description is given: seq_start / seq_len / seq_past [seqs] and max_len >= the longest
  * seq_len (host; it sizes the grid).  nsplit > 1 (tensor-core form only) deals every row block's key tiles to nsplit CTAs

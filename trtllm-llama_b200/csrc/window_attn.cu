@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(256) qkv_conv_rope_append_kernel(T* q_out, T* 
 
 constexpr int kWarps = 4;
 constexpr int kTile = 32;
-constexpr int kMaxVPerLane = 8;          // vdim <= 256
+constexpr int kMaxVPerLane = 16;         // vdim <= 512
 
 struct AttnArgs {
   const float* gate; int64_t ldg;          // gate logits [rows, >= H] or NULL
