@@ -3,7 +3,8 @@ resemble real models (random bf16 weights), beside a LLaMA engine of equal width
 ``GenerationSession`` (fp16), and every operator's distance from its roofline.
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs; every timed run works on tensors far larger than L2 or is
-preceded by an L2 flush (a 256 MB fill).  Roofline denominators: MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 burst)."""
+preceded by an L2 flush (a 256 MB fill).  Whole steps are timed from an idle device (synchronise, then the start event);
+single operators with the flush still running when the start event is enqueued (``_time_kernel``).  Roofline denominators: MEASURED_PEAKS.json (copy bandwidth, cuBLAS bf16 burst)."""
 from __future__ import annotations
 
 import json
@@ -240,6 +241,25 @@ def _time(torch, fn, steps, warmup, flush):
     return sorted(ts)[len(ts) // 2]
 
 
+def _time_kernel(torch, fn, steps, warmup, flush):
+    """One operator alone: as ``_time``, but the L2 flush is enqueued right before the start event WITHOUT a host synchronise
+    in between, so the host's launch latency (tens of microseconds of Python and ctypes per call, which a single launch
+    after a synchronise would carry) is hidden behind the flush and the events bracket the kernel's own time."""
+    for _ in range(max(3, warmup)):
+        fn()
+    ts = []
+    for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        flush.fill_(1)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e-3)
+    return sorted(ts)[len(ts) // 2]
+
+
 def _llama_side(torch, ops, rt, s, n_layers, res, prompt, S, B, steps, warmup, flush, peaks):
     """LLaMA (MHA, SwiGLU; fp16) of equal width / depth / feed-forward / vocabulary through ``GenerationSession``, and its
     like kernels alone.  Fills ``res``; returns (L, engine tensors' gate weight shape) for the caller's own like kernels."""
@@ -274,20 +294,20 @@ def _llama_side(torch, ops, rt, s, n_layers, res, prompt, S, B, steps, warmup, f
     x = torch.randn(S, L["hidden"], device="cuda").half()
     w = lt["layers.0.mlp.fc_gate.weight"]
     fl = 2.0 * S * w.shape[0] * w.shape[1]
-    t = _time(torch, lambda: ops.matmul_f16(x, w), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.matmul_f16(x, w), steps, warmup, flush)
     like["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     xd = x[:B].contiguous()
-    t = _time(torch, lambda: ops.matmul_f16(xd, w), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.matmul_f16(xd, w), steps, warmup, flush)
     like["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(w.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     H = L["heads"]
     qkv = torch.randn(1, S, 3 * H * 128, device="cuda").half()
     kvc = torch.zeros(B, 2, H, S + 64, 128, device="cuda", dtype=torch.float16)
     lens1 = torch.tensor([S], dtype=torch.int32, device="cuda")
-    t = _time(torch, lambda: ops.context_attention(qkv, kvc, lens1, num_heads=H, head_size=128), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.context_attention(qkv, kvc, lens1, num_heads=H, head_size=128), steps, warmup, flush)
     like["attention_prefill"] = {"us": round(t * 1e6, 1),
                                  "of_roofline": round(4.0 * S * S / 2 * 128 * H / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     qd = torch.randn(B, 3 * H * 128, device="cuda").half()
-    t = _time(torch, lambda: ops.mmha_decode(qd, kvc, S, num_heads=H, head_size=128, max_input_len=S), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.mmha_decode(qd, kvc, S, num_heads=H, head_size=128, max_input_len=S), steps, warmup, flush)
     like["attention_decode"] = {"us": round(t * 1e6, 1),
                                 "of_roofline": round(B * 2 * H * S * 128 * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     res["llama_like_kernels"] = like
@@ -341,10 +361,10 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
     own = {}
     xb = torch.randn(S, L["hidden"], device="cuda").bfloat16()
     wb = (torch.randn(w_shape[0], w_shape[1], device="cuda") * 0.02).bfloat16()
-    t = _time(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
     own["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     xf = torch.randn(B, L["hidden"], device="cuda")
-    t = _time(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
     own["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(wb.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     from .inflight import RaggedBatch
     lat, rot, Hh, page = s["kv_rank"], s["rot_dim"], s["heads"], 64
@@ -352,12 +372,12 @@ def bench_size(torch, name, steps, warmup, S=2048, B=4):
     pool = torch.randn((B * nblk * page, lat + rot), device="cuda").bfloat16()
     pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
     qa = torch.randn(S, Hh, lat + rot, device="cuda").bfloat16()
-    t = _time(torch, lambda: ops.latent_attention(qa, pool, pb, page, Hh, lat, rot, 0.07), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.latent_attention(qa, pool, pb, page, Hh, lat, rot, 0.07), steps, warmup, flush)
     fl_a = 2.0 * (S * (S + 1) / 2) * Hh * (2 * lat + rot)
     own["attention_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl_a / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
     qd2 = qa[:B].contiguous()
-    t = _time(torch, lambda: ops.latent_attention(qd2, pool, db, page, Hh, lat, rot, 0.07), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.latent_attention(qd2, pool, db, page, Hh, lat, rot, 0.07), steps, warmup, flush)
     own["attention_decode"] = {"us": round(t * 1e6, 1),
                                "of_roofline": round(B * S * (lat + rot) * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3),
                                "cache_bytes": B * S * (lat + rot) * 2, "llama_cache_bytes": B * 2 * H * S * 128 * 2}
@@ -410,10 +430,10 @@ def bench_nililix_size(torch, name, steps, warmup, S=2048, B=4):
     own = {}
     xb = torch.randn(S, L["hidden"], device="cuda").bfloat16()
     wb = (torch.randn(w_shape[0], w_shape[1], device="cuda") * 0.02).bfloat16()
-    t = _time(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.linear(xb, wb, out_dtype=torch.bfloat16), steps, warmup, flush)
     own["linear_prefill"] = {"us": round(t * 1e6, 1), "of_roofline": round(fl / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     xf = torch.randn(B, L["hidden"], device="cuda")
-    t = _time(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.linear(xf, wb, out_dtype=torch.float32), steps, warmup, flush)
     own["linear_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(wb.numel() * 2 / (peaks["hbm_gbs"] * 1e9) / t, 3)}
     H, G, d, dv, win, page = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"], 64
     nblk = -(-S // page)
@@ -422,13 +442,13 @@ def bench_nililix_size(torch, name, steps, warmup, S=2048, B=4):
     pb = RaggedBatch([([0] * S, 0, 0, list(range(nblk)))], [], "cuda")
     q = torch.randn(S, H, d, device="cuda").bfloat16()
     gate = torch.randn(S, H, device="cuda")
-    t = _time(torch, lambda: ops.window_attention(q, pool, pb, page, G, dv, 0.09, win, sink=sink, gate=gate), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.window_attention(q, pool, pb, page, G, dv, 0.09, win, sink=sink, gate=gate), steps, warmup, flush)
     keys = sum(min(p + 1, win) for p in range(S))
     own["attention_prefill"] = {"us": round(t * 1e6, 1), "keys_per_row": round(keys / S, 1),
                                 "of_roofline": round(2.0 * keys * H * (d + dv) / (peaks["bf16_tflops"] * 1e12) / t, 3)}
     db = RaggedBatch([([0], S - 1, b, list(range(b * nblk, (b + 1) * nblk))) for b in range(B)], [], "cuda")
     qd = q[:B].contiguous()
-    t = _time(torch, lambda: ops.window_attention(qd, pool, db, page, G, dv, 0.09, win, sink=sink, gate=gate[:B]), steps, warmup, flush)
+    t = _time_kernel(torch, lambda: ops.window_attention(qd, pool, db, page, G, dv, 0.09, win, sink=sink, gate=gate[:B]), steps, warmup, flush)
     cache_bytes = B * min(S, win) * G * (d + dv) * 2
     own["attention_decode"] = {"us": round(t * 1e6, 1), "of_roofline": round(cache_bytes / (peaks["hbm_gbs"] * 1e9) / t, 3),
                                "cache_bytes": cache_bytes, "llama_cache_bytes": B * 2 * L["heads"] * S * 128 * 2}
