@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kWarps * 32) window_attention_kernel(T* out, c
 //   S [16 x 64] = Q [16 x DIM] . K^T            mma.sync m16n8k16 bf16, fp32 accumulators, fragments through ldmatrix
 //   online softmax in fp32 in registers          window / causal mask per row; starts from the sink (m = sink, l = 1)
 //   O [16 x VDIM] += P [16 x 64] . V             P reused from the S registers as the A operand, V through ldmatrix.trans
-// K and V tiles arrive through a two-stage cp.async ring; positions outside [first visible of the CTA, last position of the
+// K and V tiles arrive through a two-stage cp.async ring (one barrier per tile); positions outside [first visible of the CTA, last position of the
 // CTA] are zero-filled, so nothing unwritten in the pool reaches an accumulator.  A tile that is wholly masked for a row
 // adds exact zeros and rescales by exactly 1, so a row's result does not depend on the rows it shares a CTA with.
 // ---------------------------------------------------------------------------------------------------------------
@@ -234,6 +234,12 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x in one instruction (ex2.approx: 2 ulp, -inf -> +0): the probabilities are rounded to bf16 right after
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -339,16 +345,16 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
 #pragma unroll
   for (int kk = 0; kk < DIM / 16; ++kk)
     ldsm_x4(qf[kk], qs + (warp * 16 + lane % 16) * LDQ + kk * 16 + (lane / 16) * 8);
-  if (kt0 + nsplit <= kt1) locate_tile(kt0 + nsplit, 1);
-  __syncthreads();                                      // the query tile's stage may be filled; key_row[1] is written
-
+  if (kt0 + nsplit <= kt1) locate_tile(kt0 + nsplit, 1);   // visible behind the loop's first barrier, like the end of the
+                                                           // fragment loads from the stage the query tile borrows
   int stage = 0;
   for (int kt = kt0; kt <= kt1; kt += nsplit, stage ^= 1) {
-    if (kt + nsplit <= kt1) load_tile(stage ^ 1);       // that stage was consumed before the barrier that ended the last trip
-    cp_async_commit();
-    cp_async_wait<1>();
+    // ONE barrier per tile: behind it this tile's copies have landed (every thread waited for its own), the other stage
+    // has been consumed by every warp, and the pool rows located last trip are visible — so the next tile's copies start here
+    cp_async_wait<0>();
     __syncthreads();
-    if (kt + 2 * nsplit <= kt1) locate_tile(kt + 2 * nsplit, stage);   // rows of the tile after next: read by load_tile next trip
+    if (kt + nsplit <= kt1) { load_tile(stage ^ 1); cp_async_commit(); }
+    if (kt + 2 * nsplit <= kt1) locate_tile(kt + 2 * nsplit, stage);   // read by load_tile behind the next barrier
     const __nv_bfloat16* kd = ks + stage * kMmaKeys * LDQ;
     const __nv_bfloat16* vd = vs + stage * kMmaKeys * LDV;
     const int j0 = kt * kMmaKeys;
@@ -384,7 +390,7 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
       const float m_new = fmaxf(m_r[h], mx[h]);
-      corr[h] = m_new == -INFINITY ? 1.f : exp2f(m_r[h] - m_new);     // nothing seen yet: nothing to rescale
+      corr[h] = m_new == -INFINITY ? 1.f : exp2_fast(m_r[h] - m_new); // nothing seen yet: nothing to rescale
       m_r[h] = m_new;
       mx[h] = m_new == -INFINITY ? 0.f : m_new;                       // exp2f(-inf - 0) = 0 below
     }
@@ -392,15 +398,17 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
     for (int n = 0; n < 8; ++n)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const float p = exp2f(s[n][c] - mx[c >> 1]);
+        const float p = exp2_fast(s[n][c] - mx[c >> 1]);
         s[n][c] = p;
         rs[c >> 1] += p;
       }
 #pragma unroll
     for (int h = 0; h < 2; ++h) l_r[h] = l_r[h] * corr[h] + rs[h];    // per-thread partial sums; the quad is added at the end
+    if (corr[0] != 1.f || corr[1] != 1.f) {             // once the running maxima have settled nothing is rescaled
 #pragma unroll
-    for (int n = 0; n < VDIM / 8; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      for (int n = 0; n < VDIM / 8; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
     }
 #pragma unroll
     for (int kk = 0; kk < kMmaKeys / 16; ++kk) {
@@ -417,7 +425,6 @@ __global__ void __launch_bounds__(128, 3) window_attention_mma_kernel(__nv_bfloa
         mma_bf16_16816(o[2 * np + 1], pa, b[2], b[3]);
       }
     }
-    __syncthreads();                                    // this stage may be overwritten by the load issued next trip
   }
   cp_async_wait<0>();
   if (nsplit > 1) {
