@@ -11,8 +11,12 @@
 //                       the rows staged once per CTA in shared memory as bf16, and reduces with shuffles.  Rows are
 //                       dealt to the warps of the whole grid round-robin, so the chip reads one contiguous window of W.
 //
+//   linear_dot_kernel   few output columns in fp32 (a router's logits): one CTA per row, 16 columns at a time in registers.
+//
 // All walk k in one fixed order per output element, so a token's result is the same wherever it stands in a batch.
 // blockIdx.z walks a batch of independent problems (per-head absorbed projections, block-diagonal gates).
+// Routed experts use the same kernels: the tile kernels walk a plan that maps tile rows to (token, choice) pairs and tiles
+// to experts (tb_moe_linear), the streaming kernel runs one pair per batch element against its expert (tb_moe_gemv).
 #include <cuda_bf16.h>
 
 #include <algorithm>

@@ -1,6 +1,7 @@
 // Routed-expert feed-forward over a ragged batch: the router's choice, the plan that sorts (token, choice) pairs by
-// expert, and the weighted sum of the chosen experts' outputs.  The expert products themselves are tb_moe_linear
-// (linear.cu): the tile kernels of tb_linear walking the plan.
+// expert, and the weighted sum of the chosen experts' outputs.  The expert products themselves are elsewhere: the tcgen05
+// kernel in grouped mode (gemm_tc.cu, tb_gemm_tc_bf16_grouped) for prompt-sized bf16 steps, the tile kernels of tb_linear
+// walking the plan (linear.cu, tb_moe_linear) for fp32, and one streaming product per pair (tb_moe_gemv) for generation steps.
 //
 //   moe_route_kernel    one warp per token: s = sigmoid(logit); choice = s + correction; experts form `groups` equal
 //                       groups of neighbours, a group scores the sum of its two largest choices, only the `keep` best
